@@ -15,7 +15,8 @@ extern "C" {
 
 #define WF_SEQ_LATENT_ATTENTION 0  /* sliding-window attention over a cached low-rank latent + one shared rotated key part */
 #define WF_SEQ_DELTA 1             /* gated delta rule with short convolutions */
-#define WF_SEQ_GQA_ATTENTION 2     /* grouped-query softmax attention over cached per-head keys and values (no rotation) */
+#define WF_SEQ_GQA_ATTENTION 2     /* grouped-query softmax attention over cached per-head keys and values */
+#define WF_SEQ_SSD 3               /* state-space recurrence with one scalar decay per head (short convolution, gated grouped norm) */
 
 /* how a layer wraps its sublayers */
 #define WF_SEQ_BLOCK_SANDWICH 0    /* x += norm_b(sub(conv(norm_a(x)))): grouped norms before and after, input convolution with carried tail */
@@ -27,6 +28,13 @@ extern "C" {
 #define WF_SEQ_FF_DENSE 2
 #define WF_SEQ_ACT_SILU 0          /* silu(g) * u */
 #define WF_SEQ_ACT_CLAMPED 1       /* g = min(g, limit), u = clamp(u, -limit, limit); g * sigmoid(1.702 g) * (u + 1) */
+#define WF_SEQ_ACT_GELU_TANH 2     /* gelu(g) * u, gelu in its tanh form */
+
+/* wf_seq_layer.qk_norm of grouped-query attention */
+#define WF_SEQ_QKNORM_NONE 0
+#define WF_SEQ_QKNORM_UNIT 1       /* each head divided by its root mean square */
+#define WF_SEQ_QKNORM_HEAD 2       /* the same, times a weight vector of the head size shared by all heads (tensors mix.q.norm, mix.k.norm) */
+#define WF_SEQ_QKNORM_FULL 3       /* RMS norm over the whole projection before the split into heads, weight of that size */
 
 typedef struct wf_seq_layer {
     int type;
@@ -53,6 +61,32 @@ typedef struct wf_seq_layer {
     float router_scale;            /* the weights are multiplied by this (0 is read as 1) */
     int shared_ff;                 /* > 0: a shared expert of this size runs for every token, times sigmoid(w_sg x) */
     float shared_limit;
+    /* grouped-query attention, further: rope_dims > 0 rotates the first rope_dims entries of every query and key head (after the norm;
+     * the cache holds rotated keys), pairs (2i, 2i + 1) when rope_interleaved else (i, i + rope_dims / 2), angle pos * rope_base^(-2i / rope_dims).
+     * chunk > 0: key j is visible to query i only when floor(i / chunk) == floor(j / chunk) (besides j <= i and the window).
+     * softcap > 0: score <- softcap * tanh(score / softcap) after the scale.  rel_rows > 0: a learned bias rel[bucket(i - j), h] (tensor
+     * mix.rel [rel_rows, heads]) is added after the cap; bucket(n) = n below rel_rows / 2, then logarithmic steps that reach the last
+     * row at distance rel_far.  sink: the softmax denominator carries an extra 1 (a key with score 0 and no value).
+     * qk_norm: WF_SEQ_QKNORM_*.  proj_bias: 1 = q, k, v and output biases, 2 = q, k, v only.  head_gate: 1 = one sigmoid gate per head
+     * (mix.g [heads, W]), 2 = one per output element (mix.g [heads * vdim, W]). */
+    int rope_interleaved, chunk, rel_rows, sink;
+    float softcap, rel_far;
+    /* delta rule, further: decay_channels = 1: one decay per head AND key channel (the decay projection has heads * dim outputs, dt_bias
+     * that many entries, A_log stays per head).  decay_rank / gate_rank > 0: that projection is a product of two matrices
+     * (mix.a1 [rank, W], mix.a2 [outputs, rank]; mix.g1, mix.g2) instead of mix.a / mix.g.  gate_act: 0 silu, 1 sigmoid. */
+    int decay_channels, decay_rank, gate_rank, gate_act;
+    /* WF_SEQ_SSD: heads of vdim channels, state size `dim`, `kv_heads` groups of input / output maps (B, C) shared by heads / kv_heads
+     * heads each, `conv` taps (with bias), the gated output normalised in out_norm_groups equal parts.  Tensors mix.in [2 inner + 2 groups
+     * dim + heads, W] laid out [z | x | B | C | dt], mix.conv, mix.conv.b, mix.dt_bias, mix.A_log, mix.D, mix.norm, mix.o. */
+    int out_norm_groups;
+    /* a second mixer beside this one: `pair` > 0 is the index of its descriptor in the layer array (at or behind n_layers); both read the
+     * same input and the mixer's output is mix_scale * this + pair_scale * that.  This mixer's tensors are then named 'l<i>.mix.left.*',
+     * the other's 'l<i>.mix.right.*'. */
+    int pair;
+    float mix_scale, pair_scale;
+    /* tied = 1: the layer has no tensors of its own and uses those of layer tied_to (an earlier layer with the same descriptor); its
+     * cache rows and its state are its own. */
+    int tied, tied_to;
 } wf_seq_layer;
 
 typedef struct wf_seq_config {
@@ -67,6 +101,10 @@ typedef struct wf_seq_config {
     float residual_mult;           /* WF_SEQ_BLOCK_POST */
     int pos_embed;                 /* 1: a sinusoidal position vector is added to the embedding (entry 2i sin, 2i + 1 cos of p * pos_base^(-2i / width)) */
     float pos_base;
+    int n_extra;                   /* mixer descriptors behind the n_layers layer entries (the second mixers of paired layers) */
+    float embed_scale;             /* the embedding row is multiplied by this (0 is read as 1) */
+    int norm_weights;              /* WF_SEQ_BLOCK_POST: 1 = the norms have weight vectors of the width instead of a single gain */
+    int tied_head;                 /* 1: logits are products with the embedding table itself; there is no 'head' tensor */
 } wf_seq_config;
 
 typedef struct wf_seq_engine wf_seq_engine;

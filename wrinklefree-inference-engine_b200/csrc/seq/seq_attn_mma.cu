@@ -402,6 +402,8 @@ bool gqa_attn_mma_usable(const GqaDims& D, const PagedCache& pc) {
            ((long long)pc.page_size * D.d) % 8 == 0 && D.G <= 65535;
 }
 
+bool gqa_attn_mma_takes(const GqaDims& D) { return D.chunk == 0 && D.softcap == 0.f && !D.rel && !D.sink && !D.gate_elem; }
+
 size_t gqa_attn_mma_workspace(int rows, int splits, int dv) { return (size_t)rows * splits * (dv + 2) * sizeof(float); }
 
 int launch_gqa_attn_mma(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, float* workspace, int splits,

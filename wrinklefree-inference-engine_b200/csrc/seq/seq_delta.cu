@@ -1,5 +1,7 @@
-// Gated delta rule: a per-head matrix state S [d, dv] in float that every token first decays, then corrects along its key
-// (u = beta (v - S^T k), S += k u^T) and finally reads with its query (o = S^T q).  The state is carried per sequence slot across steps.
+// Gated delta rule: a per-head matrix state S [d, dv] in float that every token first decays (one factor per head, or one per head and key
+// row), then corrects along its key (u = beta (v - S^T k), S += k u^T) and finally reads with its query (o = S^T q).  The same kernel
+// without the correction (u = beta v) is the state-space recurrence S = a S + dt B x^T, y = S^T C with k = B, q = C, v = x, beta = dt.
+// The state is carried per sequence slot across steps.
 #include "seq_kernels.cuh"
 
 namespace wf {
@@ -23,10 +25,47 @@ __global__ void delta_prep_kernel(DeltaDims D, float* __restrict__ qkv, int ld, 
         const float inv = (v < D.Hk ? qscale : 1.f) / sqrtf(ss + 1e-6f);
         for (int c = lane; c < D.d; c += 32) x[c] *= inv;
     }
-    for (int h = threadIdx.x; h < D.H; h += blockDim.x) {
-        beta[(size_t)i * D.H + h] = sigmoid_f(b_raw[(size_t)i * ldb + h]);
-        const float sp = softplus_f(a_raw[(size_t)i * lda + h] + to_f(dt_bias[h]));
-        decay[(size_t)i * D.H + h] = expf(-expf(to_f(A_log[h])) * sp);
+    for (int h = threadIdx.x; h < D.H; h += blockDim.x) beta[(size_t)i * D.H + h] = sigmoid_f(b_raw[(size_t)i * ldb + h]);
+    const int nd = D.vec_decay ? D.H * D.d : D.H;         // one decay per head, or per head and key channel
+    for (int k = threadIdx.x; k < nd; k += blockDim.x) {
+        const int h = D.vec_decay ? k / D.d : k;
+        const float sp = softplus_f(a_raw[(size_t)i * lda + k] + to_f(dt_bias[k]));
+        decay[(size_t)i * nd + k] = expf(-expf(to_f(A_log[h])) * sp);
+    }
+}
+
+// state-space recurrence: the step size and the decay of every head
+template <typename T>
+__global__ void ssd_prep_kernel(int n, int H, const float* __restrict__ dt_raw, int ld, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
+                                float* __restrict__ step, float* __restrict__ decay) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= n * H) return;
+    const int i = k / H, h = k - i * H;
+    const float z = dt_raw[(size_t)i * ld + h] + to_f(dt_bias[h]);
+    const float sp = z > 20.f ? z : log1pf(expf(z));     // softplus without a clamp
+    step[k] = sp;
+    decay[k] = expf(-expf(to_f(A_log[h])) * sp);
+}
+
+// one block per (token, norm group): v = (o + D_h x) * silu(z), divided by the root mean square of the group, times the weight
+template <typename T>
+__global__ void ssd_post_kernel(int H, int dv, int groups, const float* __restrict__ o, const float* __restrict__ x, int ldx, const float* __restrict__ z, int ldz,
+                                const T* __restrict__ Dskip, const T* __restrict__ w, float eps, T* __restrict__ y) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x, g = blockIdx.y;
+    const int inner = H * dv, gw = inner / groups;
+    float ss = 0.f;
+    for (int c = g * gw + threadIdx.x; c < (g + 1) * gw; c += blockDim.x) {
+        const float xv = x[(size_t)i * ldx + c];
+        const float v = (o[(size_t)i * inner + c] + to_f(Dskip[c / dv]) * xv) * silu_f(z[(size_t)i * ldz + c]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)gw + eps);
+    for (int c = g * gw + threadIdx.x; c < (g + 1) * gw; c += blockDim.x) {
+        const float xv = x[(size_t)i * ldx + c];
+        const float v = (o[(size_t)i * inner + c] + to_f(Dskip[c / dv]) * xv) * silu_f(z[(size_t)i * ldz + c]);
+        y[(size_t)i * inner + c] = from_f<T>(v * inv * to_f(w[c]));
     }
 }
 
@@ -41,13 +80,15 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
 // while the current group runs, so the per-token chain is only register math, shared-memory broadcasts and two quad reductions.
 // DR_PARTS = 8 (16 columns per block): short per-token chains and twice the blocks, for portions of many tokens;
 // DR_PARTS = 4 (32 columns): wider, better coalesced state rows, for single decoded tokens where the state traffic is the cost.
-template <int DPT, int DR_PARTS>
+// VEC: the decay is a vector over the key rows (staged per token like k and q) instead of one number per token.
+// DELTA: the write is corrected by what the state already holds along the key (the delta rule); without it u = beta v.
+template <int DPT, int DR_PARTS, bool VEC, bool DELTA>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDims D, const float* __restrict__ qkv, int ld,
                                                                          const float* __restrict__ beta, const float* __restrict__ decay,
                                                                          float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
     constexpr int DR_COLS = DR_THREADS / DR_PARTS;
     extern __shared__ float sm[];
-    const int tile_floats = 2 * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][d], q [TT][d], v [TT][32], beta [TT], decay [TT]
+    const int tile_floats = (VEC ? 3 : 2) * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][d], q [TT][d], v [TT][cols], beta [TT], decay [TT], vector decay [TT][d]
     const int sq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
     const int tid = threadIdx.x, p = tid % DR_PARTS, jl = tid / DR_PARTS, col = col0 + jl;
     const bool col_ok = col < D.dv;
@@ -60,19 +101,22 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
         const int i = p + DR_PARTS * m;
         s[m] = (col_ok && i < D.d) ? S[(size_t)i * D.dv + col] : 0.f;
     }
-    const int q_off = kh * D.d, k_off = (D.Hk + kh) * D.d, v_off = 2 * D.Hk * D.d + h * D.dv;
+    const int q_off = (D.q_off >= 0 ? D.q_off : 0) + kh * D.d, k_off = (D.k_off >= 0 ? D.k_off : D.Hk * D.d) + kh * D.d,
+              v_off = (D.v_off >= 0 ? D.v_off : 2 * D.Hk * D.d) + h * D.dv;
     auto stage = [&](int buf, int t0) {
         float* ks = sm + (size_t)buf * tile_floats;
         float* qs = ks + DR_TT * D.d;
         float* vs = qs + DR_TT * D.d;
         float* bs = vs + DR_TT * DR_COLS;
         float* gs = bs + DR_TT;
+        float* gv = gs + DR_TT;
         const int tt = len - t0 < DR_TT ? len - t0 : DR_TT;
         for (int idx = tid; idx < tt * D.d; idx += blockDim.x) {
             const int t = idx / D.d, c = idx - t * D.d;
             const float* row = qkv + (size_t)(start + t0 + t) * ld;
             cp_async4(ks + idx, row + k_off + c);
             cp_async4(qs + idx, row + q_off + c);
+            if (VEC) cp_async4(gv + idx, decay + ((size_t)(start + t0 + t) * D.H + h) * D.d + c);
         }
         for (int idx = tid; idx < tt * DR_COLS; idx += blockDim.x) {
             const int t = idx / DR_COLS, c = idx % DR_COLS;
@@ -81,7 +125,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
         }
         if (tid < tt) {
             cp_async4(bs + tid, beta + (size_t)(start + t0 + tid) * D.H + h);
-            cp_async4(gs + tid, decay + (size_t)(start + t0 + tid) * D.H + h);
+            if (!VEC) cp_async4(gs + tid, decay + (size_t)(start + t0 + tid) * D.H + h);
         }
         cp_async_commit();
     };
@@ -97,20 +141,32 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
         const float* vs = qs + DR_TT * D.d;
         const float* bs = vs + DR_TT * DR_COLS;
         const float* gs = bs + DR_TT;
+        const float* gv = gs + DR_TT;
         for (int t = 0; t < tt; ++t) {
             const float* kt = ks + t * D.d;
             const float* qt = qs + t * D.d;
-            const float g = gs[t];
-            float r[4] = {0.f, 0.f, 0.f, 0.f};                // four chains: the sum over this thread's rows is not one dependent sequence
+            const float* gt = gv + t * D.d;
+            const float g = VEC ? 1.f : gs[t];
+            if (VEC) {                                        // the rows decay first, each by its own factor
 #pragma unroll
-            for (int m = 0; m < DPT; ++m) {
-                const int i = p + DR_PARTS * m;
-                if (i < D.d) r[m & 3] = fmaf(s[m], kt[i], r[m & 3]);
+                for (int m = 0; m < DPT; ++m) {
+                    const int i = p + DR_PARTS * m;
+                    if (i < D.d) s[m] *= gt[i];
+                }
             }
-            float rs = (r[0] + r[1]) + (r[2] + r[3]);
-            rs += __shfl_xor_sync(0xffffffffu, rs, 1);
-            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-            if (DR_PARTS == 8) rs += __shfl_xor_sync(0xffffffffu, rs, 4);
+            float rs = 0.f;
+            if (DELTA) {
+                float r[4] = {0.f, 0.f, 0.f, 0.f};            // four chains: the sum over this thread's rows is not one dependent sequence
+#pragma unroll
+                for (int m = 0; m < DPT; ++m) {
+                    const int i = p + DR_PARTS * m;
+                    if (i < D.d) r[m & 3] = fmaf(s[m], kt[i], r[m & 3]);
+                }
+                rs = (r[0] + r[1]) + (r[2] + r[3]);
+                rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+                rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+                if (DR_PARTS == 8) rs += __shfl_xor_sync(0xffffffffu, rs, 4);
+            }
             const float u = bs[t] * (vs[t * DR_COLS + jl] - g * rs);
             float out[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -137,7 +193,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
 
 template <typename T>
 __global__ void delta_post_kernel(DeltaDims D, const float* __restrict__ o, const T* __restrict__ w, float eps, const float* __restrict__ g, int ldg,
-                                  T* __restrict__ y) {
+                                  T* __restrict__ y, int act) {
     const int i = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     for (int h = blockIdx.y * nw + warp; h < D.H; h += gridDim.y * nw) {
@@ -146,8 +202,10 @@ __global__ void delta_post_kernel(DeltaDims D, const float* __restrict__ o, cons
         for (int c = lane; c < D.dv; c += 32) ss += x[c] * x[c];
         ss = warp_sum(ss);
         const float inv = 1.f / sqrtf(ss / (float)D.dv + eps);
-        for (int c = lane; c < D.dv; c += 32)
-            y[((size_t)i * D.H + h) * D.dv + c] = from_f<T>(x[c] * inv * to_f(w[c]) * silu_f(g[(size_t)i * ldg + (size_t)h * D.dv + c]));
+        for (int c = lane; c < D.dv; c += 32) {
+            const float z = g[(size_t)i * ldg + (size_t)h * D.dv + c];
+            y[((size_t)i * D.H + h) * D.dv + c] = from_f<T>(x[c] * inv * to_f(w[c]) * (act ? sigmoid_f(z) : silu_f(z)));
+        }
     }
 }
 
@@ -162,36 +220,68 @@ int launch_delta_prep(int dt, const DeltaDims& D, int n, float* qkv, int ld, con
     return launch_check(cudaGetLastError(), "delta_prep");
 }
 
-int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
+namespace {
+template <bool VEC, bool DELTA>
+int delta_rule_launch(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
                       size_t slot_stride, float* o, cudaStream_t s) {
-    if (b.nseq <= 0) return WF_OK;
-    if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
     const bool decode = b.n == b.nseq;                     // every sequence brings one token
     const int parts = decode ? 4 : 8, cols = DR_THREADS / parts;
     dim3 grid(b.nseq, D.H, (D.dv + cols - 1) / cols);
-    const size_t smem = 2 * ((size_t)2 * DR_TT * D.d + DR_TT * cols + 2 * DR_TT) * sizeof(float);   // two token groups
+    const size_t smem = 2 * ((size_t)(VEC ? 3 : 2) * DR_TT * D.d + DR_TT * cols + 2 * DR_TT) * sizeof(float);   // two token groups
     static DevOnce once;
     if (once.need()) {
-        cudaFuncSetAttribute(delta_rule_kernel<32, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(delta_rule_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(delta_rule_kernel<32, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(delta_rule_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+#define DR_ATTR(dp, pa) cudaFuncSetAttribute(delta_rule_kernel<dp, pa, VEC, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
+        DR_ATTR(8, 8); DR_ATTR(16, 8); DR_ATTR(32, 8); DR_ATTR(64, 8); DR_ATTR(8, 4); DR_ATTR(16, 4); DR_ATTR(32, 4); DR_ATTR(64, 4);
+#undef DR_ATTR
     }
     const int dpt = (D.d + parts - 1) / parts;
-#define DR_LAUNCH(dp, pa) delta_rule_kernel<dp, pa><<<grid, DR_THREADS, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o)
-    if (D.d > 256 || smem > 96 * 1024) { set_error("delta: key dimension %d above the supported 256", D.d); return WF_ERR_UNSUPPORTED; }
+#define DR_LAUNCH(dp, pa) delta_rule_kernel<dp, pa, VEC, DELTA><<<grid, DR_THREADS, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o)
+    if (D.d > 256 || smem > 160 * 1024) { set_error("delta: key dimension %d above the supported 256", D.d); return WF_ERR_UNSUPPORTED; }
     if (decode) { if (dpt <= 8) DR_LAUNCH(8, 4); else if (dpt <= 16) DR_LAUNCH(16, 4); else if (dpt <= 32) DR_LAUNCH(32, 4); else DR_LAUNCH(64, 4); }
     else { if (dpt <= 8) DR_LAUNCH(8, 8); else if (dpt <= 16) DR_LAUNCH(16, 8); else if (dpt <= 32) DR_LAUNCH(32, 8); else DR_LAUNCH(64, 8); }
 #undef DR_LAUNCH
     return launch_check(cudaGetLastError(), "delta_rule");
 }
+}  // namespace
 
-int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s) {
+int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
+                      size_t slot_stride, float* o, cudaStream_t s) {
+    if (b.nseq <= 0) return WF_OK;
+    if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
+    if (D.no_delta) {
+        if (D.vec_decay) { set_error("delta: the plain recurrence takes one decay per head"); return WF_ERR_UNSUPPORTED; }
+        return delta_rule_launch<false, false>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s);
+    }
+    return D.vec_decay ? delta_rule_launch<true, true>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s)
+                       : delta_rule_launch<false, true>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s);
+}
+
+int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s, int act) {
     if (n <= 0) return WF_OK;
     const dim3 grid(n, n < 64 ? (D.H + 3) / 4 : 1);
-    if (dt == WF_BF16) delta_post_kernel<<<grid, 128, 0, s>>>(D, o, (const __nv_bfloat16*)w, eps, g, ldg, (__nv_bfloat16*)y);
-    else delta_post_kernel<<<grid, 128, 0, s>>>(D, o, (const float*)w, eps, g, ldg, (float*)y);
+    if (dt == WF_BF16) delta_post_kernel<<<grid, 128, 0, s>>>(D, o, (const __nv_bfloat16*)w, eps, g, ldg, (__nv_bfloat16*)y, act);
+    else delta_post_kernel<<<grid, 128, 0, s>>>(D, o, (const float*)w, eps, g, ldg, (float*)y, act);
     return launch_check(cudaGetLastError(), "delta_post");
+}
+
+int launch_ssd_prep(int dt, int n, int H, const float* dt_raw, int ld, const void* A_log, const void* dt_bias, float* step, float* decay, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    const int blocks = (n * H + 127) / 128;
+    if (dt == WF_BF16) ssd_prep_kernel<<<blocks, 128, 0, s>>>(n, H, dt_raw, ld, (const __nv_bfloat16*)A_log, (const __nv_bfloat16*)dt_bias, step, decay);
+    else ssd_prep_kernel<<<blocks, 128, 0, s>>>(n, H, dt_raw, ld, (const float*)A_log, (const float*)dt_bias, step, decay);
+    return launch_check(cudaGetLastError(), "ssd_prep");
+}
+
+int launch_ssd_post(int dt, int n, int H, int dv, int groups, const float* o, const float* x, int ldx, const float* z, int ldz, const void* Dskip,
+                    const void* w, float eps, void* y, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (groups <= 0 || (H * dv) % groups) { set_error("ssd: %d channels not divisible into %d norm groups", H * dv, groups); return WF_ERR_INVALID; }
+    const int gw = H * dv / groups;
+    const int threads = gw >= 1024 ? 256 : (gw >= 256 ? 128 : 64);
+    const dim3 grid(n, groups);
+    if (dt == WF_BF16) ssd_post_kernel<<<grid, threads, 0, s>>>(H, dv, groups, o, x, ldx, z, ldz, (const __nv_bfloat16*)Dskip, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)y);
+    else ssd_post_kernel<<<grid, threads, 0, s>>>(H, dv, groups, o, x, ldx, z, ldz, (const float*)Dskip, (const float*)w, eps, (float*)y);
+    return launch_check(cudaGetLastError(), "ssd_post");
 }
 
 }  // namespace seq

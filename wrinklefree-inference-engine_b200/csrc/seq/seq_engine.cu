@@ -5,6 +5,7 @@
 #include "seq_kernels.cuh"
 #include "../pager.h"
 #include "wf_seq.h"
+#include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -48,6 +49,15 @@ struct LayerState {
     void *ugu = nullptr, *ud = nullptr;
     int uff = 0;
     float ulimit = 0.f;
+    // attention: weights of the query / key norms, the bias table as loaded [rel_rows, heads] and expanded by distance (float [rel_n, heads])
+    void *q_norm_w = nullptr, *k_norm_w = nullptr, *rel = nullptr;
+    float* rel_dist = nullptr;
+    int rel_n = 0;
+    // recurrences: second factors of two-matrix projections (decay, gate), column offsets of the gate / write-strength / decay parts in the
+    // fused projection; state-space: convolution bias, skip weights
+    void *a2 = nullptr, *g2 = nullptr, *conv_b = nullptr, *Dskip = nullptr;
+    int g_col = 0, b_col = 0, a_col = 0, n_decay = 0;
+    int pair_state = 0;       // index of the second mixer's state in the engine's layer array
     // state slot offsets (floats)
     size_t st_canon1 = 0, st_canon2 = 0, st_conv = 0, st_S = 0;
 };
@@ -80,6 +90,8 @@ struct wf_seq_engine {
           *decay = nullptr, *od = nullptr, *z = nullptr, *wts = nullptr, *gu = nullptr, *yexp = nullptr;
     void *hperm = nullptr, *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
     float *gate = nullptr, *ugu = nullptr, *uy = nullptr;      // head gates; the every-token unit's [gate | up] rows and its output
+    float *y2 = nullptr;              // output of the second mixer of a paired layer
+    float *gfull = nullptr, *afull = nullptr;   // recurrences: gate and decay logits when they are products of two matrices
     void* uhmid = nullptr;
     int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
     int P = 0;                        // padded expert-row bound
@@ -144,15 +156,35 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
     }
     if (c.block_form != WF_SEQ_BLOCK_SANDWICH && c.block_form != WF_SEQ_BLOCK_POST) { set_error("wf_seq_create: block form %d", c.block_form); return WF_ERR_INVALID; }
     if (c.page_size <= 0 || c.max_pages <= 0 || c.slots <= 0 || c.max_step_tokens <= 0) { set_error("wf_seq_create: page / slot / step sizes must be positive"); return WF_ERR_INVALID; }
-    for (int i = 0; i < c.n_layers; ++i) {
+    if (c.n_extra < 0) { set_error("wf_seq_create: %d extra mixers", c.n_extra); return WF_ERR_INVALID; }
+    for (int i = 0; i < c.n_layers + c.n_extra; ++i) {
         const wf_seq_layer& l = L[i];
         if (l.heads <= 0 || l.dim <= 0 || l.vdim <= 0) { set_error("layer %d: heads / dim / vdim must be positive", i); return WF_ERR_INVALID; }
+        if (i >= c.n_layers && (l.pair || l.has_ff || l.tied)) { set_error("mixer %d: a second mixer has no pair, feed-forward or tie of its own", i); return WF_ERR_INVALID; }
+        if (l.pair && (l.pair < c.n_layers || l.pair >= c.n_layers + c.n_extra)) { set_error("layer %d: pair %d is not a second-mixer entry", i, l.pair); return WF_ERR_INVALID; }
+        if (l.tied) {
+            const wf_seq_layer* src = l.tied_to >= 0 && l.tied_to < i ? &L[l.tied_to] : nullptr;
+            if (!src || src->tied || src->type != l.type || src->heads != l.heads || src->dim != l.dim || src->vdim != l.vdim || src->kv_heads != l.kv_heads ||
+                src->has_ff != l.has_ff || src->ff != l.ff || (src->pair != 0) != (l.pair != 0) || src->conv != l.conv) {
+                set_error("layer %d: tied_to %d must name an earlier untied layer of the same shape", i, l.tied_to); return WF_ERR_INVALID;
+            }
+            if (l.pair && (L[l.pair].type != L[src->pair].type || L[l.pair].heads != L[src->pair].heads || L[l.pair].dim != L[src->pair].dim ||
+                           L[l.pair].vdim != L[src->pair].vdim || L[l.pair].kv_heads != L[src->pair].kv_heads || L[l.pair].conv != L[src->pair].conv)) {
+                set_error("layer %d: its second mixer differs in shape from that of layer %d", i, l.tied_to); return WF_ERR_INVALID;
+            }
+        }
         if (l.type == WF_SEQ_LATENT_ATTENTION) {
             if (l.kv_rank <= 0 || l.rot_dim < 0 || l.window < 1 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1)) { set_error("layer %d: latent attention sizes", i); return WF_ERR_INVALID; }
         } else if (l.type == WF_SEQ_DELTA) {
-            if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.conv < 1) { set_error("layer %d: delta sizes", i); return WF_ERR_INVALID; }
+            if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.conv < 1 || l.decay_rank < 0 || l.gate_rank < 0) { set_error("layer %d: delta sizes", i); return WF_ERR_INVALID; }
+        } else if (l.type == WF_SEQ_SSD) {
+            if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.conv < 1 || l.out_norm_groups < 1 || (l.heads * l.vdim) % l.out_norm_groups) { set_error("layer %d: state-space sizes", i); return WF_ERR_INVALID; }
         } else if (l.type == WF_SEQ_GQA_ATTENTION) {
             if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.window < 1) { set_error("layer %d: attention sizes", i); return WF_ERR_INVALID; }
+            if (l.qk_norm < 0 || l.qk_norm > 3 || l.rope_dims < 0 || (l.rope_dims & 1) || l.rope_dims > l.dim || l.chunk < 0 || l.rel_rows < 0 || l.softcap < 0.f ||
+                (l.rel_rows > 0 && (l.rel_rows < 2 || !(l.rel_far > (float)(l.rel_rows / 2)))) || l.head_gate < 0 || l.head_gate > 2 || l.proj_bias < 0 || l.proj_bias > 2) {
+                set_error("layer %d: attention options", i); return WF_ERR_INVALID;
+            }
             if (l.kv_from >= 0) {
                 const wf_seq_layer* src = l.kv_from < i ? &L[l.kv_from] : nullptr;
                 if (!src || src->type != WF_SEQ_GQA_ATTENTION || src->kv_from >= 0 || src->kv_heads != l.kv_heads || src->dim != l.dim || src->vdim != l.vdim) {
@@ -163,7 +195,7 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
         } else { set_error("layer %d: unknown mixer type %d", i, l.type); return WF_ERR_INVALID; }
         if (l.has_ff != WF_SEQ_FF_NONE && l.has_ff != WF_SEQ_FF_ROUTED && l.has_ff != WF_SEQ_FF_DENSE) { set_error("layer %d: feed-forward kind %d", i, l.has_ff); return WF_ERR_INVALID; }
         if (l.has_ff == WF_SEQ_FF_DENSE && l.ff <= 0) { set_error("layer %d: dense feed-forward size", i); return WF_ERR_INVALID; }
-        if (l.has_ff && (l.ff_act < 0 || l.ff_act > 1 || l.shared_ff < 0)) { set_error("layer %d: feed-forward activation / shared size", i); return WF_ERR_INVALID; }
+        if (l.has_ff && (l.ff_act < 0 || l.ff_act > 2 || l.shared_ff < 0)) { set_error("layer %d: feed-forward activation / shared size", i); return WF_ERR_INVALID; }
         if (l.has_ff == WF_SEQ_FF_ROUTED) {
             const int N = l.experts + l.identity;
             if (l.experts < 0 || l.identity < 0 || N <= 0 || l.top < 1 || l.top > N || l.groups < 1 || N % l.groups || l.keep < 1 || l.keep > l.groups || (l.experts > 0 && l.ff <= 0)) {
@@ -252,7 +284,7 @@ GemmArgs lin(const void* A, int a_f32, int lda, const void* B, int ldb, void* C,
 }
 
 // h (post-convolution input, storage type [n, W]) -> y float [n, W]
-int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b) {
+int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     const wf_seq_layer& c = L.c;
     const int W = e->cfg.width, n = b.n, H = c.heads, per = c.dim + c.rot_dim, nq = H * per, nkv = c.kv_rank + c.rot_dim, nv = H * c.vdim;
     cudaStream_t s = e->stream;
@@ -298,43 +330,86 @@ int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b) {
     }
     if ((rc = launch_gate_mul(e->dt, e->ov, nv, e->proj + nq + nkv, L.np, 0, n, nv, e->og, nv, s))) return rc;
     mark(e, "latent.gate");
-    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, out, 1, W, n, W, nv), s);
     mark(e, "latent.out_gemm");
     return rc;
 }
 
-int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b) {
+int run_delta(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     const wf_seq_layer& c = L.c;
     const int W = e->cfg.width, n = b.n, H = c.heads, nv = H * c.vdim, C = L.C;
     cudaStream_t s = e->stream;
     int rc;
     DeltaDims D{H, c.kv_heads, c.dim, c.vdim};
-    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | k | v | g | b | a]
+    D.vec_decay = c.decay_channels ? 1 : 0;
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | k | v | g or g1 | b | a or a1]
     mark(e, "delta.proj_gemm");
+    // gate and decay logits: columns of the fused projection, or a second small product on its low-rank columns
+    const float* g_raw = e->proj + L.g_col;
+    int ldg = L.np;
+    if (c.gate_rank > 0) {
+        if ((rc = launch_gemm(e->dt, lin(e->proj + L.g_col, 1, L.np, L.g2, c.gate_rank, e->gfull, 1, nv, n, nv, c.gate_rank), s))) return rc;
+        g_raw = e->gfull; ldg = nv;
+    }
+    const float* a_raw = e->proj + L.a_col;
+    int lda = L.np;
+    if (c.decay_rank > 0) {
+        if ((rc = launch_gemm(e->dt, lin(e->proj + L.a_col, 1, L.np, L.a2, c.decay_rank, e->afull, 1, L.n_decay, n, L.n_decay, c.decay_rank), s))) return rc;
+        a_raw = e->afull; lda = L.n_decay;
+    }
+    if (c.gate_rank > 0 || c.decay_rank > 0) mark(e, "delta.lowrank_gemm");
     float* st_conv = e->state + L.st_conv;
     if ((rc = launch_causal_taps(e->dt, b, e->proj, L.np, L.conv_w, c.conv, C, st_conv, e->slot_stride, 0, 1, nullptr, 0, e->qkvc, C, s))) return rc;
     if ((rc = launch_taps_state(b, e->proj, L.np, c.conv, C, st_conv, e->slot_stride, s))) return rc;
-    const float* g_raw = e->proj + C;
-    const float* b_raw = g_raw + nv;
-    const float* a_raw = b_raw + H;
-    if ((rc = launch_delta_prep(e->dt, D, n, e->qkvc, C, a_raw, L.np, b_raw, L.np, L.A_log, L.dt_bias, e->beta, e->decay, s))) return rc;
+    const float* b_raw = e->proj + L.b_col;
+    if ((rc = launch_delta_prep(e->dt, D, n, e->qkvc, C, a_raw, lda, b_raw, L.np, L.A_log, L.dt_bias, e->beta, e->decay, s))) return rc;
     mark(e, "delta.conv+prep");
     if ((rc = launch_delta_rule(b, D, e->qkvc, C, e->beta, e->decay, e->state + L.st_S, e->slot_stride, e->od, s))) return rc;
     mark(e, "delta.rule");
-    if ((rc = launch_delta_post(e->dt, D, n, e->od, L.onorm, e->cfg.eps, g_raw, L.np, e->og, s))) return rc;
+    if ((rc = launch_delta_post(e->dt, D, n, e->od, L.onorm, e->cfg.eps, g_raw, ldg, e->og, s, c.gate_act))) return rc;
     mark(e, "delta.post");
-    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
+    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, out, 1, W, n, W, nv), s);
     mark(e, "delta.out_gemm");
     return rc;
 }
 
+// state-space recurrence: [z | x | B | C | dt] projection -> convolution + silu over x | B | C -> step sizes and decays -> the recurrence
+// (the delta-rule kernel without its correction: key = B, query = C, value = x, write strength = dt) -> skip, gate, grouped norm -> output
+int run_ssd(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
+    const wf_seq_layer& c = L.c;
+    const int W = e->cfg.width, n = b.n, H = c.heads, inner = H * c.vdim, GN = c.kv_heads * c.dim, C = L.C;
+    cudaStream_t s = e->stream;
+    int rc;
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;
+    mark(e, "ssd.proj_gemm");
+    float* st_conv = e->state + L.st_conv;
+    const float* xbc_raw = e->proj + inner;
+    if ((rc = launch_causal_taps(e->dt, b, xbc_raw, L.np, L.conv_w, c.conv, C, st_conv, e->slot_stride, 0, 1, nullptr, 0, e->qkvc, C, s, L.conv_b))) return rc;
+    if ((rc = launch_taps_state(b, xbc_raw, L.np, c.conv, C, st_conv, e->slot_stride, s))) return rc;
+    if ((rc = launch_ssd_prep(e->dt, n, H, e->proj + 2 * inner + 2 * GN, L.np, L.A_log, L.dt_bias, e->beta, e->decay, s))) return rc;
+    mark(e, "ssd.conv+prep");
+    DeltaDims D{H, c.kv_heads, c.dim, c.vdim};
+    D.no_delta = 1; D.v_off = 0; D.k_off = inner; D.q_off = inner + GN;
+    if ((rc = launch_delta_rule(b, D, e->qkvc, C, e->beta, e->decay, e->state + L.st_S, e->slot_stride, e->od, s))) return rc;
+    mark(e, "ssd.recurrence");
+    if ((rc = launch_ssd_post(e->dt, n, H, c.vdim, c.out_norm_groups, e->od, e->qkvc, C, e->proj, L.np, L.Dskip, L.onorm, e->cfg.eps, e->og, s))) return rc;
+    mark(e, "ssd.post");
+    rc = launch_gemm(e->dt, lin(e->og, 0, inner, L.wo, inner, out, 1, W, n, W, inner), s);
+    mark(e, "ssd.out_gemm");
+    return rc;
+}
+
 // h_t -> y float [n, W].  In the post form the output projection's bias is NOT added here: the norm kernel that follows takes it
-int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
+int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     const wf_seq_layer& c = L.c;
     const int W = e->cfg.width, n = b.n, nv = c.heads * c.vdim;
     cudaStream_t s = e->stream;
     int rc;
     GqaDims D{c.heads, c.kv_heads, c.dim, c.vdim, c.scale, c.dist_exp, c.window, c.qk_norm, c.v_norm};
+    D.rope_dims = c.rope_dims; D.rope_interleaved = c.rope_interleaved; D.rope_base = c.rope_base;
+    D.q_norm_w = L.q_norm_w; D.k_norm_w = L.k_norm_w;
+    D.chunk = c.chunk; D.sink = c.sink; D.gate_elem = c.head_gate == 2; D.softcap = c.softcap;
+    D.rel = L.rel_dist; D.rel_n = L.rel_n;
     const LayerState& src = c.kv_from >= 0 ? e->layers[c.kv_from] : L;        // whose cache rows this layer reads
     PagedCache pc{e->pool, e->page_stride, src.cache_off, e->cfg.page_size, e->d_block_table, e->pt.max_blocks};
     if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | k | v | g]
@@ -342,7 +417,7 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
     if ((rc = launch_gqa_prep(e->dt, b, D, e->proj, L.np, L.k_off, L.v_off, L.g_off, L.qb, L.kb, L.vb, e->cfg.eps, pc, e->qn, c.head_gate ? e->gate : nullptr, s))) return rc;
     mark(e, "attn.prep+kv_write");
     const float* gate = c.head_gate ? e->gate : nullptr;
-    if (e->dt == WF_BF16 && e->attn_mma >= 1 && gqa_attn_mma_usable(D, pc)) {
+    if (e->dt == WF_BF16 && e->attn_mma >= 1 && gqa_attn_mma_usable(D, pc) && gqa_attn_mma_takes(D)) {
         // decoding (one token per sequence): few CTAs with long key ranges, so the keys are cut until there are about four resident
         // waves of CTAs (two are resident per SM): the machine is covered and the last wave's tail stays short.
         // The cut depends on the batch size and the pool only, never on the lengths: a captured step stays valid.
@@ -359,15 +434,32 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b) {
         if ((rc = launch_gqa_attn_mma(b, D, e->qn, gate, pc, e->og, e->gqa_ws, splits, s))) return rc;
     } else if ((rc = launch_gqa_attn(e->dt, b, D, e->qn, gate, pc, e->og, s))) return rc;
     mark(e, "attn.attention");
-    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, e->y, 1, W, n, W, nv), s);
-    if (!rc && L.ob && e->cfg.block_form != WF_SEQ_BLOCK_POST) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
+    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, out, 1, W, n, W, nv), s);
+    // the single-gain norm of the post form takes the bias itself, except for paired mixers (their outputs are combined first)
+    if (!rc && L.ob && !(e->cfg.block_form == WF_SEQ_BLOCK_POST && !e->cfg.norm_weights && !L.c.pair && out == e->y)) rc = launch_add_bias(e->dt, out, W, L.ob, n, W, s);
     mark(e, "attn.out_gemm");
     return rc;
 }
 
+int run_one_mixer(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
+    switch (L.c.type) {
+        case WF_SEQ_GQA_ATTENTION: return run_gqa(e, L, b, out);
+        case WF_SEQ_LATENT_ATTENTION: return run_latent(e, L, b, out);
+        case WF_SEQ_SSD: return run_ssd(e, L, b, out);
+        default: return run_delta(e, L, b, out);
+    }
+}
+
+// h_t -> y.  A paired layer runs its two mixers one after the other on the same input (they share the projection workspaces) and
+// combines their outputs in float.
 int run_mixer(wf_seq_engine* e, LayerState& L, const Batch& b) {
-    if (L.c.type == WF_SEQ_GQA_ATTENTION) return run_gqa(e, L, b);
-    return L.c.type == WF_SEQ_LATENT_ATTENTION ? run_latent(e, L, b) : run_delta(e, L, b);
+    int rc;
+    if ((rc = run_one_mixer(e, L, b, e->y))) return rc;
+    if (!L.c.pair) return WF_OK;
+    if ((rc = run_one_mixer(e, e->layers[L.pair_state], b, e->y2))) return rc;
+    rc = launch_axpby(e->y, L.c.mix_scale, e->y2, L.c.pair_scale, (size_t)b.n * e->cfg.width, e->stream);
+    mark(e, "pair.combine");
+    return rc;
 }
 
 // the gated unit every token runs (dense feed-forward / shared expert): h_t -> out float [n, W]
@@ -484,20 +576,23 @@ int run_layers_post(wf_seq_engine* e, const StepView& v) {
     const float mult = e->cfg.residual_mult, eps = e->cfg.eps;
     cudaStream_t s = e->stream;
     int rc;
+    const float escale = e->cfg.embed_scale != 0.f ? e->cfg.embed_scale : 1.f;
+    const bool vec = e->cfg.norm_weights != 0;            // weight vectors (one launch of the grouped norm with one group) or single gains
     if (e->cfg.pos_embed) { if ((rc = launch_embed_pos(e->dt, e->embed, v.tokens, v.b.tok_pos, n, W, e->cfg.pos_base, e->x, e->h_t, s))) return rc; }
-    else {
-        if ((rc = launch_embed_f32(e->dt, e->embed, v.tokens, n, W, e->x, s))) return rc;
-        if ((rc = launch_round_rows(e->dt, e->x, n, W, e->h_t, s))) return rc;
-    }
+    else if ((rc = launch_embed_f32(e->dt, e->embed, v.tokens, n, W, e->x, s, escale, e->h_t))) return rc;
     mark(e, "embed");
     for (int li = 0; li < e->cfg.n_layers; ++li) {
         LayerState& L = e->layers[li];
         if ((rc = run_mixer(e, L, v.b))) return rc;
-        if ((rc = launch_scalar_rmsnorm(e->dt, e->y, W, L.ob, L.norm1, mult, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s))) return rc;
+        if (vec) rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm1, 1, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s);
+        else rc = launch_scalar_rmsnorm(e->dt, e->y, W, L.c.pair ? nullptr : L.ob, L.norm1, mult, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s);
+        if (rc) return rc;
         mark(e, "norm+residual");
         if (L.c.has_ff) {
             if ((rc = run_ff(e, L, v.b))) return rc;
-            if ((rc = launch_scalar_rmsnorm(e->dt, e->y, W, nullptr, L.norm2, mult, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s))) return rc;
+            if (vec) rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm2, 1, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s);
+            else rc = launch_scalar_rmsnorm(e->dt, e->y, W, nullptr, L.norm2, mult, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s);
+            if (rc) return rc;
             mark(e, "norm+residual");
         }
         if (e->layer_tap) {
@@ -550,7 +645,8 @@ int run_head(wf_seq_engine* e, const StepView& v, int nwant) {
     const int W = e->cfg.width;
     int rc;
     if ((rc = ensure_logits(e, nwant))) return rc;
-    if (e->cfg.block_form == WF_SEQ_BLOCK_POST) rc = launch_scalar_rmsnorm(e->dt, e->x, W, nullptr, e->final_norm, 1.f, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
+    if (e->cfg.block_form == WF_SEQ_BLOCK_POST && e->cfg.norm_weights) rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, 1, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
+    else if (e->cfg.block_form == WF_SEQ_BLOCK_POST) rc = launch_scalar_rmsnorm(e->dt, e->x, W, nullptr, e->final_norm, 1.f, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
     else rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, e->cfg.norm_groups, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
     if (rc) return rc;
     rc = launch_gemm(e->dt, lin(e->xn, 0, W, e->head, W, e->logits, 1, e->cfg.vocab, nwant, e->cfg.vocab, W), e->stream);
@@ -621,135 +717,194 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     if (cuda_check(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking), "stream")) { delete e; return WF_ERR_CUDA; }
     TRY(dalloc_t(e, &e->embed, (size_t)c.vocab * W));
     const bool post = c.block_form == WF_SEQ_BLOCK_POST;
-    const size_t norm_elems = post ? 1 : W;              // the post form's norms have a single gain
+    const size_t norm_elems = post && !c.norm_weights ? 1 : W;   // the post form's norms have a single gain unless the model says otherwise
     TRY(dalloc_t(e, &e->final_norm, norm_elems));
-    TRY(dalloc_t(e, &e->head, (size_t)c.vocab * W));
     add_tensor(e, "embed", e->embed, (size_t)c.vocab * W);
     add_tensor(e, "final.norm", e->final_norm, norm_elems);
-    add_tensor(e, "head", e->head, (size_t)c.vocab * W);
+    if (c.tied_head) e->head = e->embed;
+    else { TRY(dalloc_t(e, &e->head, (size_t)c.vocab * W)); add_tensor(e, "head", e->head, (size_t)c.vocab * W); }
     // maxima over layers for the shared workspaces
     size_t max_np = 1, max_hd = 1, max_hr = 1, max_hrot = 1, max_hv = 1, max_C = 1, max_H = 1, max_N = 1, max_top = 1, max_E = 1, max_ff = 1, max_uff = 0, max_gqa_dv = 0;
     long long cache_elems = 0;
     size_t st = 0;
-    e->layers.resize(c.n_layers);
-    for (int li = 0; li < c.n_layers; ++li) {
-        LayerState& L = e->layers[li];
-        L.c = layers[li];
+    e->layers.resize(c.n_layers + c.n_extra);
+    size_t max_gate = 1, max_decay = 1, max_gfull = 0, max_afull = 0;
+    bool own = true;                 // false while a tied layer is laid out: it allocates and names nothing, its weights are its source's
+    auto walloc = [&](void** ptr, size_t count) -> int { return own ? dalloc_t(e, ptr, count) : WF_OK; };
+    auto name = [&](const std::string& n, void* dst, size_t count) { if (own) add_tensor(e, n, dst, count); };
+    // one mixer: weights named mp + '<tensor>', its part of a cache page, its part of a state slot
+    auto setup_mixer = [&](LayerState& L, const std::string& mp, int index) -> int {
         const wf_seq_layer& l = L.c;
-        const std::string p = "l" + std::to_string(li) + ".";
-        L.norm1 = L.norm2 = L.norm1b = L.norm2b = L.canon1 = L.canon2 = nullptr;
-        if (post) {
-            TRY(dalloc_t(e, &L.norm1, 1)); add_tensor(e, p + "norm1", L.norm1, 1);
-            if (l.has_ff) { TRY(dalloc_t(e, &L.norm2, 1)); add_tensor(e, p + "norm2", L.norm2, 1); }
-        } else {
-            void** norms[4] = {&L.norm1, &L.norm1b, &L.norm2, &L.norm2b};
-            const char* norm_names[4] = {"norm1", "norm1b", "norm2", "norm2b"};
-            for (int k = 0; k < (l.has_ff ? 4 : 2); ++k) { TRY(dalloc_t(e, norms[k], W)); add_tensor(e, p + norm_names[k], *norms[k], W); }
-            TRY(dalloc_t(e, &L.canon1, (size_t)W * taps)); add_tensor(e, p + "canon1", L.canon1, (size_t)W * taps);
-            L.st_canon1 = st; st += (size_t)(taps - 1) * W;
-            if (l.has_ff) {
-                TRY(dalloc_t(e, &L.canon2, (size_t)W * taps)); add_tensor(e, p + "canon2", L.canon2, (size_t)W * taps);
-                L.st_canon2 = st; st += (size_t)(taps - 1) * W;
-            }
-        }
+        int rc = WF_OK;
+#define TRYL(x) do { if ((rc = (x))) return rc; } while (0)
         const size_t nv = (size_t)l.heads * l.vdim;
-        TRY(dalloc_t(e, &L.wo, (size_t)W * nv)); add_tensor(e, p + "mix.o", L.wo, (size_t)W * nv);
+        TRYL(walloc(&L.wo, (size_t)W * nv)); name(mp + "o", L.wo, (size_t)W * nv);
         if (l.type == WF_SEQ_GQA_ATTENTION) {
             const size_t nq = (size_t)l.heads * l.dim, nk = (size_t)l.kv_heads * l.dim, nvk = (size_t)l.kv_heads * l.vdim;
-            const bool own = l.kv_from < 0;
+            const bool ownkv = l.kv_from < 0;
+            const size_t ng = l.head_gate == 2 ? nv : (size_t)l.heads;
             size_t off = nq;
-            if (own) { L.k_off = (int)off; off += nk; L.v_off = (int)off; off += nvk; }
-            if (l.head_gate) { L.g_off = (int)off; off += l.heads; }
+            if (ownkv) { L.k_off = (int)off; off += nk; L.v_off = (int)off; off += nvk; }
+            if (l.head_gate) { L.g_off = (int)off; off += ng; }
             L.np = (int)off;
-            TRY(dalloc_t(e, &L.wp, (size_t)L.np * W));
-            add_tensor(e, p + "mix.q", L.wp, nq * W);
-            if (own) {
-                add_tensor(e, p + "mix.k", at(e, L.wp, (size_t)L.k_off * W), nk * W);
-                add_tensor(e, p + "mix.v", at(e, L.wp, (size_t)L.v_off * W), nvk * W);
+            TRYL(walloc(&L.wp, (size_t)L.np * W));
+            name(mp + "q", L.wp, nq * W);
+            if (ownkv) {
+                name(mp + "k", at(e, L.wp, (size_t)L.k_off * W), nk * W);
+                name(mp + "v", at(e, L.wp, (size_t)L.v_off * W), nvk * W);
             }
-            if (l.head_gate) add_tensor(e, p + "mix.g", at(e, L.wp, (size_t)L.g_off * W), (size_t)l.heads * W);
+            if (l.head_gate) name(mp + "g", at(e, L.wp, (size_t)L.g_off * W), ng * W);
             if (l.proj_bias) {
-                TRY(dalloc_t(e, &L.qb, nq)); add_tensor(e, p + "mix.q.b", L.qb, nq);
-                if (own) {
-                    TRY(dalloc_t(e, &L.kb, nk)); add_tensor(e, p + "mix.k.b", L.kb, nk);
-                    TRY(dalloc_t(e, &L.vb, nvk)); add_tensor(e, p + "mix.v.b", L.vb, nvk);
+                TRYL(walloc(&L.qb, nq)); name(mp + "q.b", L.qb, nq);
+                if (ownkv) {
+                    TRYL(walloc(&L.kb, nk)); name(mp + "k.b", L.kb, nk);
+                    TRYL(walloc(&L.vb, nvk)); name(mp + "v.b", L.vb, nvk);
                 }
-                TRY(dalloc_t(e, &L.ob, W)); add_tensor(e, p + "mix.o.b", L.ob, W);
+                if (l.proj_bias == 1) { TRYL(walloc(&L.ob, W)); name(mp + "o.b", L.ob, W); }
             }
-            if (own) {
+            if (l.qk_norm >= WF_SEQ_QKNORM_HEAD) {
+                const size_t wq = l.qk_norm == WF_SEQ_QKNORM_FULL ? nq : (size_t)l.dim, wk = l.qk_norm == WF_SEQ_QKNORM_FULL ? nk : (size_t)l.dim;
+                TRYL(walloc(&L.q_norm_w, wq)); name(mp + "q.norm", L.q_norm_w, wq);
+                TRYL(walloc(&L.k_norm_w, wk)); name(mp + "k.norm", L.k_norm_w, wk);      // a layer that reads another's cache still names it: unused
+            }
+            if (l.rel_rows > 0) {
+                TRYL(walloc(&L.rel, (size_t)l.rel_rows * l.heads)); name(mp + "rel", L.rel, (size_t)l.rel_rows * l.heads);
+                // beyond rel_far every distance falls into the last row: rel_far + 1 rows by distance are all there is
+                L.rel_n = (int)ceilf(l.rel_far) + 1;
+                if (own) TRYL(dalloc_n(e, &L.rel_dist, (size_t)L.rel_n * l.heads));
+            }
+            if (ownkv) {
                 // every layer's part of a page starts 16-byte aligned
                 cache_elems = (cache_elems + 7) / 8 * 8;
                 L.cache_off = cache_elems;
                 cache_elems += (long long)c.page_size * (nk + nvk);
             }
             max_hd = std::max(max_hd, nq); max_gqa_dv = std::max(max_gqa_dv, (size_t)l.vdim);
+            max_gate = std::max(max_gate, ng);
         } else if (l.type == WF_SEQ_LATENT_ATTENTION) {
             const size_t nq = (size_t)l.heads * (l.dim + l.rot_dim), nkv = l.kv_rank + l.rot_dim;
             L.np = (int)(nq + nkv + nv);
-            TRY(dalloc_t(e, &L.wp, (size_t)L.np * W));
-            add_tensor(e, p + "mix.q", L.wp, nq * W);
-            add_tensor(e, p + "mix.dkv", at(e, L.wp, nq * W), nkv * W);
-            add_tensor(e, p + "mix.g", at(e, L.wp, (nq + nkv) * W), nv * W);
-            TRY(dalloc_t(e, &L.dkv_norm, l.kv_rank)); add_tensor(e, p + "mix.dkv.norm", L.dkv_norm, l.kv_rank);
-            TRY(dalloc_t(e, &L.uk, (size_t)l.heads * l.dim * l.kv_rank)); add_tensor(e, p + "mix.uk", L.uk, (size_t)l.heads * l.dim * l.kv_rank);
-            TRY(dalloc_t(e, &L.ukT, (size_t)l.heads * l.dim * l.kv_rank));
-            TRY(dalloc_t(e, &L.uv, nv * l.kv_rank)); add_tensor(e, p + "mix.uv", L.uv, nv * l.kv_rank);
+            TRYL(walloc(&L.wp, (size_t)L.np * W));
+            name(mp + "q", L.wp, nq * W);
+            name(mp + "dkv", at(e, L.wp, nq * W), nkv * W);
+            name(mp + "g", at(e, L.wp, (nq + nkv) * W), nv * W);
+            TRYL(walloc(&L.dkv_norm, l.kv_rank)); name(mp + "dkv.norm", L.dkv_norm, l.kv_rank);
+            TRYL(walloc(&L.uk, (size_t)l.heads * l.dim * l.kv_rank)); name(mp + "uk", L.uk, (size_t)l.heads * l.dim * l.kv_rank);
+            TRYL(walloc(&L.ukT, (size_t)l.heads * l.dim * l.kv_rank));
+            TRYL(walloc(&L.uv, nv * l.kv_rank)); name(mp + "uv", L.uv, nv * l.kv_rank);
             L.cache_off = cache_elems;
             cache_elems += (long long)c.page_size * nkv;
             max_hd = std::max(max_hd, (size_t)l.heads * l.dim); max_hr = std::max(max_hr, (size_t)l.heads * l.kv_rank);
             max_hrot = std::max(max_hrot, (size_t)l.heads * std::max(l.rot_dim, 1));
-        } else {
-            const size_t nqk = (size_t)l.kv_heads * l.dim;
-            L.C = (int)(2 * nqk + nv);
-            L.np = (int)(L.C + nv + 2 * l.heads);
-            TRY(dalloc_t(e, &L.wp, (size_t)L.np * W));
-            add_tensor(e, p + "mix.q", L.wp, nqk * W);
-            add_tensor(e, p + "mix.k", at(e, L.wp, nqk * W), nqk * W);
-            add_tensor(e, p + "mix.v", at(e, L.wp, 2 * nqk * W), nv * W);
-            add_tensor(e, p + "mix.g", at(e, L.wp, (size_t)L.C * W), nv * W);
-            add_tensor(e, p + "mix.b", at(e, L.wp, ((size_t)L.C + nv) * W), (size_t)l.heads * W);
-            add_tensor(e, p + "mix.a", at(e, L.wp, ((size_t)L.C + nv + l.heads) * W), (size_t)l.heads * W);
-            TRY(dalloc_t(e, &L.conv_w, (size_t)L.C * l.conv));
-            add_tensor(e, p + "mix.q.conv", L.conv_w, nqk * l.conv);
-            add_tensor(e, p + "mix.k.conv", at(e, L.conv_w, nqk * l.conv), nqk * l.conv);
-            add_tensor(e, p + "mix.v.conv", at(e, L.conv_w, 2 * nqk * l.conv), nv * l.conv);
-            TRY(dalloc_t(e, &L.A_log, l.heads)); add_tensor(e, p + "mix.A_log", L.A_log, l.heads);
-            TRY(dalloc_t(e, &L.dt_bias, l.heads)); add_tensor(e, p + "mix.dt_bias", L.dt_bias, l.heads);
-            TRY(dalloc_t(e, &L.onorm, l.vdim)); add_tensor(e, p + "mix.norm", L.onorm, l.vdim);
+        } else if (l.type == WF_SEQ_SSD) {
+            // [z | x | B | C | dt]: x, B and C are the convolved channels
+            const size_t GN = (size_t)l.kv_heads * l.dim;
+            L.C = (int)(nv + 2 * GN);
+            L.np = (int)(2 * nv + 2 * GN + l.heads);
+            TRYL(walloc(&L.wp, (size_t)L.np * W)); name(mp + "in", L.wp, (size_t)L.np * W);
+            TRYL(walloc(&L.conv_w, (size_t)L.C * l.conv)); name(mp + "conv", L.conv_w, (size_t)L.C * l.conv);
+            TRYL(walloc(&L.conv_b, L.C)); name(mp + "conv.b", L.conv_b, L.C);
+            TRYL(walloc(&L.dt_bias, l.heads)); name(mp + "dt_bias", L.dt_bias, l.heads);
+            TRYL(walloc(&L.A_log, l.heads)); name(mp + "A_log", L.A_log, l.heads);
+            TRYL(walloc(&L.Dskip, l.heads)); name(mp + "D", L.Dskip, l.heads);
+            TRYL(walloc(&L.onorm, nv)); name(mp + "norm", L.onorm, nv);
             L.st_conv = st; st += (size_t)(l.conv - 1) * L.C;
             L.st_S = st; st += (size_t)l.heads * l.dim * l.vdim;
             max_C = std::max(max_C, (size_t)L.C);
+        } else {
+            // [q | k | v | gate (or its first factor) | write strength | decay (or its first factor)]
+            const size_t nqk = (size_t)l.kv_heads * l.dim;
+            L.C = (int)(2 * nqk + nv);
+            L.n_decay = l.decay_channels ? l.heads * l.dim : l.heads;
+            const size_t g_rows = l.gate_rank > 0 ? (size_t)l.gate_rank : nv, a_rows = l.decay_rank > 0 ? (size_t)l.decay_rank : (size_t)L.n_decay;
+            L.g_col = L.C; L.b_col = (int)(L.C + g_rows); L.a_col = L.b_col + l.heads;
+            L.np = (int)(L.a_col + a_rows);
+            TRYL(walloc(&L.wp, (size_t)L.np * W));
+            name(mp + "q", L.wp, nqk * W);
+            name(mp + "k", at(e, L.wp, nqk * W), nqk * W);
+            name(mp + "v", at(e, L.wp, 2 * nqk * W), nv * W);
+            name(mp + (l.gate_rank > 0 ? "g1" : "g"), at(e, L.wp, (size_t)L.g_col * W), g_rows * W);
+            name(mp + "b", at(e, L.wp, (size_t)L.b_col * W), (size_t)l.heads * W);
+            name(mp + (l.decay_rank > 0 ? "a1" : "a"), at(e, L.wp, (size_t)L.a_col * W), a_rows * W);
+            if (l.gate_rank > 0) { TRYL(walloc(&L.g2, nv * l.gate_rank)); name(mp + "g2", L.g2, nv * l.gate_rank); max_gfull = std::max(max_gfull, nv); }
+            if (l.decay_rank > 0) { TRYL(walloc(&L.a2, (size_t)L.n_decay * l.decay_rank)); name(mp + "a2", L.a2, (size_t)L.n_decay * l.decay_rank); max_afull = std::max(max_afull, (size_t)L.n_decay); }
+            TRYL(walloc(&L.conv_w, (size_t)L.C * l.conv));
+            name(mp + "q.conv", L.conv_w, nqk * l.conv);
+            name(mp + "k.conv", at(e, L.conv_w, nqk * l.conv), nqk * l.conv);
+            name(mp + "v.conv", at(e, L.conv_w, 2 * nqk * l.conv), nv * l.conv);
+            TRYL(walloc(&L.A_log, l.heads)); name(mp + "A_log", L.A_log, l.heads);
+            TRYL(walloc(&L.dt_bias, L.n_decay)); name(mp + "dt_bias", L.dt_bias, L.n_decay);
+            TRYL(walloc(&L.onorm, l.vdim)); name(mp + "norm", L.onorm, l.vdim);
+            L.st_conv = st; st += (size_t)(l.conv - 1) * L.C;
+            L.st_S = st; st += (size_t)l.heads * l.dim * l.vdim;
+            max_C = std::max(max_C, (size_t)L.C);
+            max_decay = std::max(max_decay, (size_t)L.n_decay);
         }
         max_np = std::max(max_np, (size_t)L.np); max_hv = std::max(max_hv, nv); max_H = std::max(max_H, (size_t)l.heads);
+        (void)index;
+#undef TRYL
+        return WF_OK;
+    };
+    const size_t lnorm = post ? norm_elems : (size_t)W;
+    for (int li = 0; li < c.n_layers; ++li) {
+        LayerState& L = e->layers[li];
+        own = !layers[li].tied;
+        if (!own) L = e->layers[layers[li].tied_to];      // the source's weight pointers; offsets of cache and state are assigned anew below
+        L.c = layers[li];
+        const wf_seq_layer& l = L.c;
+        const std::string p = "l" + std::to_string(li) + ".";
+        if (own) L.norm1 = L.norm2 = L.norm1b = L.norm2b = L.canon1 = L.canon2 = nullptr;
+        if (post) {
+            TRY(walloc(&L.norm1, lnorm)); name(p + "norm1", L.norm1, lnorm);
+            if (l.has_ff) { TRY(walloc(&L.norm2, lnorm)); name(p + "norm2", L.norm2, lnorm); }
+        } else {
+            void** norms[4] = {&L.norm1, &L.norm1b, &L.norm2, &L.norm2b};
+            const char* norm_names[4] = {"norm1", "norm1b", "norm2", "norm2b"};
+            for (int k = 0; k < (l.has_ff ? 4 : 2); ++k) { TRY(walloc(norms[k], W)); name(p + norm_names[k], *norms[k], W); }
+            TRY(walloc(&L.canon1, (size_t)W * taps)); name(p + "canon1", L.canon1, (size_t)W * taps);
+            L.st_canon1 = st; st += (size_t)(taps - 1) * W;
+            if (l.has_ff) {
+                TRY(walloc(&L.canon2, (size_t)W * taps)); name(p + "canon2", L.canon2, (size_t)W * taps);
+                L.st_canon2 = st; st += (size_t)(taps - 1) * W;
+            }
+        }
+        TRY(setup_mixer(L, l.pair ? p + "mix.left." : p + "mix.", li));
+        if (l.pair) {
+            LayerState& R = e->layers[l.pair];
+            if (!own) R = e->layers[e->layers[l.tied_to].pair_state];
+            R.c = layers[l.pair];
+            L.pair_state = l.pair;
+            TRY(setup_mixer(R, p + "mix.right.", l.pair));
+        }
         if (l.has_ff == WF_SEQ_FF_DENSE) {
             L.uff = l.ff; L.ulimit = l.ff_limit;
-            TRY(dalloc_t(e, &L.ugu, (size_t)2 * l.ff * W)); TRY(dalloc_t(e, &L.ud, (size_t)W * l.ff));
-            add_tensor(e, p + "mlp.gate", L.ugu, (size_t)l.ff * W);
-            add_tensor(e, p + "mlp.up", at(e, L.ugu, (size_t)l.ff * W), (size_t)l.ff * W);
-            add_tensor(e, p + "mlp.down", L.ud, (size_t)W * l.ff);
+            TRY(walloc(&L.ugu, (size_t)2 * l.ff * W)); TRY(walloc(&L.ud, (size_t)W * l.ff));
+            name(p + "mlp.gate", L.ugu, (size_t)l.ff * W);
+            name(p + "mlp.up", at(e, L.ugu, (size_t)l.ff * W), (size_t)l.ff * W);
+            name(p + "mlp.down", L.ud, (size_t)W * l.ff);
             max_uff = std::max(max_uff, (size_t)l.ff);
         } else if (l.has_ff == WF_SEQ_FF_ROUTED) {
             const size_t N = l.experts + l.identity;
             L.nz = (int)N + (l.shared_ff > 0 ? 1 : 0);
-            TRY(dalloc_t(e, &L.router, (size_t)L.nz * W)); add_tensor(e, p + "mlp.router", L.router, N * W);
+            TRY(walloc(&L.router, (size_t)L.nz * W)); name(p + "mlp.router", L.router, N * W);
             if (l.shared_ff > 0) {
                 L.uff = l.shared_ff; L.ulimit = l.shared_limit;
-                add_tensor(e, p + "mlp.shared.sg", at(e, L.router, N * W), W);
-                TRY(dalloc_t(e, &L.ugu, (size_t)2 * l.shared_ff * W)); TRY(dalloc_t(e, &L.ud, (size_t)W * l.shared_ff));
-                add_tensor(e, p + "mlp.shared.gate", L.ugu, (size_t)l.shared_ff * W);
-                add_tensor(e, p + "mlp.shared.up", at(e, L.ugu, (size_t)l.shared_ff * W), (size_t)l.shared_ff * W);
-                add_tensor(e, p + "mlp.shared.down", L.ud, (size_t)W * l.shared_ff);
+                name(p + "mlp.shared.sg", at(e, L.router, N * W), W);
+                TRY(walloc(&L.ugu, (size_t)2 * l.shared_ff * W)); TRY(walloc(&L.ud, (size_t)W * l.shared_ff));
+                name(p + "mlp.shared.gate", L.ugu, (size_t)l.shared_ff * W);
+                name(p + "mlp.shared.up", at(e, L.ugu, (size_t)l.shared_ff * W), (size_t)l.shared_ff * W);
+                name(p + "mlp.shared.down", L.ud, (size_t)W * l.shared_ff);
                 max_uff = std::max(max_uff, (size_t)l.shared_ff);
             }
-            TRY(dalloc_t(e, &L.correction, N)); add_tensor(e, p + "mlp.correction", L.correction, N);
+            TRY(walloc(&L.correction, N)); name(p + "mlp.correction", L.correction, N);
             if (l.experts > 0) {
-                TRY(dalloc_t(e, &L.wgu, (size_t)l.experts * 2 * l.ff * W));
-                TRY(dalloc_t(e, &L.wd, (size_t)l.experts * W * l.ff));
+                TRY(walloc(&L.wgu, (size_t)l.experts * 2 * l.ff * W));
+                TRY(walloc(&L.wd, (size_t)l.experts * W * l.ff));
                 for (int x = 0; x < l.experts; ++x) {
                     const std::string ep = p + "mlp.e" + std::to_string(x) + ".";
-                    add_tensor(e, ep + "gate", at(e, L.wgu, (size_t)x * 2 * l.ff * W), (size_t)l.ff * W);
-                    add_tensor(e, ep + "up", at(e, L.wgu, ((size_t)x * 2 + 1) * l.ff * W), (size_t)l.ff * W);
-                    add_tensor(e, ep + "down", at(e, L.wd, (size_t)x * W * l.ff), (size_t)W * l.ff);
+                    name(ep + "gate", at(e, L.wgu, (size_t)x * 2 * l.ff * W), (size_t)l.ff * W);
+                    name(ep + "up", at(e, L.wgu, ((size_t)x * 2 + 1) * l.ff * W), (size_t)l.ff * W);
+                    name(ep + "down", at(e, L.wd, (size_t)x * W * l.ff), (size_t)W * l.ff);
                 }
             }
             max_N = std::max(max_N, (size_t)L.nz); max_top = std::max(max_top, (size_t)l.top); max_E = std::max(max_E, (size_t)std::max(l.experts, 1));
@@ -758,6 +913,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
             e->P = std::max(e->P, P);
         }
     }
+    own = true;
     // cache pool and state slots
     e->page_stride = cache_elems;
     TRY(dalloc_t(e, &e->pool, (size_t)std::max<long long>(cache_elems, 1) * c.max_pages));
@@ -779,10 +935,13 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     TRY(dalloc_t(e, &e->olat, (size_t)T * max_hr)); TRY(dalloc_n(e, &e->ov, (size_t)T * max_hv)); TRY(dalloc_t(e, &e->og, (size_t)T * max_hv));
     e->attn_ws_rows = 4 * 148;
     if (e->dt == WF_BF16 && max_hr > 1) TRY(dalloc_bytes(e, (void**)&e->attn_ws, (size_t)e->attn_ws_rows * (max_hr + 2 * max_H) * sizeof(float)));
-    TRY(dalloc_n(e, &e->gate, (size_t)T * max_H));
+    TRY(dalloc_n(e, &e->gate, (size_t)T * std::max(max_H, max_gate)));
+    if (c.n_extra > 0) TRY(dalloc_n(e, &e->y2, (size_t)T * W));
+    if (max_gfull) TRY(dalloc_n(e, &e->gfull, (size_t)T * max_gfull));
+    if (max_afull) TRY(dalloc_n(e, &e->afull, (size_t)T * max_afull));
     if (e->dt == WF_BF16 && max_gqa_dv) { e->gqa_ws_rows = 32768; TRY(dalloc_bytes(e, (void**)&e->gqa_ws, gqa_attn_mma_workspace(e->gqa_ws_rows, 1, (int)max_gqa_dv))); }
     if (max_uff) { TRY(dalloc_n(e, &e->ugu, (size_t)T * 2 * max_uff)); TRY(dalloc_t(e, &e->uhmid, (size_t)T * max_uff)); TRY(dalloc_n(e, &e->uy, (size_t)T * W)); }
-    TRY(dalloc_n(e, &e->qkvc, (size_t)T * max_C)); TRY(dalloc_n(e, &e->beta, (size_t)T * max_H)); TRY(dalloc_n(e, &e->decay, (size_t)T * max_H));
+    TRY(dalloc_n(e, &e->qkvc, (size_t)T * max_C)); TRY(dalloc_n(e, &e->beta, (size_t)T * max_H)); TRY(dalloc_n(e, &e->decay, (size_t)T * std::max(max_H, max_decay)));
     TRY(dalloc_n(e, &e->od, (size_t)T * max_hv));
     TRY(dalloc_n(e, &e->z, (size_t)T * max_N)); TRY(dalloc_n(e, &e->ids, (size_t)T * max_top)); TRY(dalloc_n(e, &e->wts, (size_t)T * max_top));
     TRY(dalloc_n(e, &e->pair_row, (size_t)T * max_top)); TRY(dalloc_n(e, &e->counts, max_E)); TRY(dalloc_n(e, &e->plan_scratch, 2 * max_E + 1));
@@ -840,6 +999,37 @@ extern "C" int wf_seq_finalize(wf_seq_engine* e) {
     for (LayerState& L : e->layers)
         if (L.c.type == WF_SEQ_LATENT_ATTENTION)      // W_uk per head [dim, kv_rank] -> [kv_rank, dim]: the weight of q -> W_uk^T q
             if (int rc = launch_transpose_heads(e->dt, L.uk, L.c.heads, L.c.dim, L.c.kv_rank, L.ukT, e->stream)) return rc;
+    // attention bias tables: the loaded rows [rel_rows, heads] expanded to one row per distance 0 .. rel_far (later distances share the last).
+    // The bucket of a distance is computed here, once, in double: exact below rel_rows / 2, then logarithmic steps up to rel_far.
+    for (int li = 0; li < (int)e->layers.size(); ++li) {
+        LayerState& L = e->layers[li];
+        if (L.c.type != WF_SEQ_GQA_ATTENTION || L.c.rel_rows <= 0 || L.c.tied) continue;
+        if (li >= e->cfg.n_layers) {           // a second mixer: skip those whose owner is tied
+            bool tied_owner = false;
+            for (int k = 0; k < e->cfg.n_layers; ++k) if (e->layers[k].c.pair == li && e->layers[k].c.tied) tied_owner = true;
+            if (tied_owner) continue;
+        }
+        const int B = L.c.rel_rows, H = L.c.heads, half = B / 2;
+        std::vector<unsigned char> raw((size_t)B * H * e->esz);
+        if (cuda_check(cudaMemcpyAsync(raw.data(), L.rel, raw.size(), cudaMemcpyDeviceToHost, e->stream), "bias table D2H")) return WF_ERR_CUDA;
+        if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;
+        std::vector<float> tab((size_t)L.rel_n * H);
+        for (int n = 0; n < L.rel_n; ++n) {
+            int bucket = n;
+            if (n >= half) {
+                const double steps = floor(log((double)n / (double)half) / log((double)L.c.rel_far / (double)half) * (double)(B - half));
+                bucket = steps >= (double)(B - 1 - half) ? B - 1 : half + (int)steps;
+            }
+            for (int h = 0; h < H; ++h) {
+                float v;
+                if (e->dt == WF_F32) v = ((const float*)raw.data())[(size_t)bucket * H + h];
+                else { const uint32_t bits = (uint32_t)((const uint16_t*)raw.data())[(size_t)bucket * H + h] << 16; memcpy(&v, &bits, 4); }
+                tab[(size_t)n * H + h] = v;
+            }
+        }
+        if (cuda_check(cudaMemcpyAsync(L.rel_dist, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, e->stream), "bias table H2D")) return WF_ERR_CUDA;
+        if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;
+    }
     if (cuda_check(cudaStreamSynchronize(e->stream), "finalize")) return WF_ERR_CUDA;
     e->finalized = true;
     return WF_OK;
@@ -919,7 +1109,11 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
     float* result = e->y;
     const bool post = e->cfg.block_form == WF_SEQ_BLOCK_POST;
     if (post && (part == 1 || part == 4)) { set_error("wf_seq_run_part: this model's sublayers have no input convolution"); return WF_ERR_INVALID; }
-    if (part == 0 && post) {
+    if (part == 0 && post && e->cfg.norm_weights) {
+        if (cuda_check(cudaMemcpyAsync(e->x, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
+        rc = launch_group_rmsnorm(e->dt, e->x, W, L.norm1, 1, e->cfg.eps, n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s);
+        result = e->hn;
+    } else if (part == 0 && post) {
         if (cuda_check(cudaMemcpyAsync(e->x, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
         rc = launch_scalar_rmsnorm(e->dt, e->x, W, nullptr, L.norm1, e->cfg.residual_mult, e->cfg.eps, n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s);
         result = e->hn;
@@ -941,7 +1135,7 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
         if (post && cuda_check(cudaMemcpyAsync(e->x, e->hn, bytes, cudaMemcpyDeviceToDevice, s), "in")) return WF_ERR_CUDA;
         rc = launch_gate_mul(e->dt, e->hn, W, e->hn, W, 2, n, W, e->h_t, W, s);
         if (!rc) rc = part == 2 ? run_mixer(e, L, v.b) : run_ff(e, L, v.b);
-        if (!rc && part == 2 && L.ob && post) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
+        if (!rc && part == 2 && L.ob && post && !e->cfg.norm_weights && !L.c.pair) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
     } else { set_error("wf_seq_run_part: unknown part %d", part); return WF_ERR_INVALID; }
     if (rc) return rc;
     if (cuda_check(cudaMemcpyAsync(out_host, result, bytes, cudaMemcpyDeviceToHost, s), "out")) return WF_ERR_CUDA;

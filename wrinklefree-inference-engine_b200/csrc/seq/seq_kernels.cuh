@@ -9,8 +9,10 @@
 namespace wf {
 namespace seq {
 
-// x[i, :] = table[tokens[i], :] as float
-int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, int W, float* x, cudaStream_t s);
+// x[i, :] = scale * table[tokens[i], :] as float; x_t: optional T copy
+int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, int W, float* x, cudaStream_t s, float scale = 1.f, void* x_t = nullptr);
+// y = a * y + b * y2 over count floats
+int launch_axpby(float* y, float a, const float* y2, float b, size_t count, cudaStream_t s);
 // y = [res +] w * x / sqrt(mean_g(x^2) + eps) per row and per group of W / groups consecutive elements.  x, y, res float [n, W] with row
 // strides ldx / ldy (res shares ldy; y may alias res); rows: optional gather of the input AND residual rows.  y_t: optional T copy of y.
 int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
@@ -26,9 +28,11 @@ int launch_scalar_rmsnorm(int dt, const float* y, int ldy, const void* bias, con
 int launch_add_bias(int dt, float* y, int ld, const void* bias, int n, int W, cudaStream_t s);
 // causal depthwise taps over time with carried state: out_t = [identity ? in_t : 0] + sum_j w[c, j] * in_(t - taps + 1 + j), optional silu.
 // in float [n, C] (ld_in); state float [slot][taps - 1][C] (slot_stride floats between slots) = the last taps - 1 inputs of each sequence,
-// read here and rolled forward by launch_taps_state AFTER this kernel.  out: T [n, C] (out_t) and / or float (out_f).
+// read here and rolled forward by launch_taps_state AFTER this kernel.  out: T [n, C] (out_t) and / or float (out_f).  bias: optional T [C],
+// added before the activation.
 int launch_causal_taps(int dt, const Batch& b, const float* in, int ld_in, const void* w, int taps, int C, const float* state,
-                       size_t slot_stride, int identity, int silu, void* out_t, int ld_t, float* out_f, int ld_f, cudaStream_t s);
+                       size_t slot_stride, int identity, int silu, void* out_t, int ld_t, float* out_f, int ld_f, cudaStream_t s,
+                       const void* bias = nullptr);
 int launch_taps_state(const Batch& b, const float* in, int ld_in, int taps, int C, float* state, size_t slot_stride, cudaStream_t s, int skip_single = 0);
 // grouped RMS norm of x (float [n, W]) and the identity-plus-taps convolution over the normalised rows in one kernel: out_t T [n, W].
 // hn (float [n, W]) receives the normalised rows of each portion's last taps - 1 tokens, for launch_taps_state(..., skip_single = 1)
@@ -102,13 +106,25 @@ int launch_gate_mul(int dt, const float* x, int ldx, const float* g, int ldg, in
 int launch_transpose_heads(int dt, const void* in, int H, int R, int C, void* out, cudaStream_t s);
 
 // ---- grouped-query attention (seq_attn.cu) ----------------------------------------------------------------------------------------
-struct GqaDims { int H, G, d, dv; float scale, dist_exp; int window, qk_norm, v_norm; };
+// qk_norm: 0 none, 1 each head divided by its root mean square, 2 the same times a weight vector of the head size (q_norm_w / k_norm_w,
+// T [d]), 3 RMS norm over the whole projection with weights T [H * d] / [G * d].  rope_dims > 0: the first rope_dims entries of every query
+// and key head are rotated after the norm (pairs (2i, 2i + 1) when rope_interleaved, else (i, i + rope_dims / 2)).  chunk > 0: a query sees
+// only keys of its own chunk of that many positions.  softcap > 0: score <- softcap * tanh(score / softcap).  rel (float [rel_n, H], on the
+// device): bias by distance, rel[min(i - j, rel_n - 1), h], added after the cap.  sink: the softmax denominator carries an extra 1.
+// gate_elem: the gate has one entry per output element ([n, H * dv]) instead of one per head ([n, H]).
+struct GqaDims {
+    int H, G, d, dv; float scale, dist_exp; int window, qk_norm, v_norm;
+    int rope_dims = 0, rope_interleaved = 0; float rope_base = 0.f;
+    const void *q_norm_w = nullptr, *k_norm_w = nullptr;
+    int chunk = 0, sink = 0, gate_elem = 0; float softcap = 0.f;
+    const float* rel = nullptr; int rel_n = 0;
+};
 // elements one layer's keys and values take in a cache page: keys [G][page_size][d], then values [G][page_size][dv]
 long long gqa_cache_elems(const GqaDims& D, int page_size);
 // proj float [n, ld]: queries at column 0 (H * d), keys at k_off (G * d), values at v_off (G * dv), gate logits at g_off (H); negative
 // offsets: that part is absent (k_off and v_off together: the layer reads another layer's cache).  Adds the biases (T, or null), divides
 // by the root mean square per head where D says so; queries -> qn T [n, H, d]; keys / values -> the token's cache row; gate float [n, H]
-// = sigmoid of the gate logits (1 when g_off < 0; gate null: not written).
+// = sigmoid of the gate logits (1 when g_off < 0; gate null: not written); [n, H * dv] with D.gate_elem.
 int launch_gqa_prep(int dt, const Batch& b, const GqaDims& D, const float* proj, int ld, int k_off, int v_off, int g_off, const void* qb, const void* kb,
                     const void* vb, float eps, const PagedCache& pc, void* qn, float* gate, cudaStream_t s);
 // out T [n, H * dv]: per (token, head) softmax over keys j in (pos - window, pos] of q . k_j * scale - slope_h * (pos - j), weighted value
@@ -119,21 +135,32 @@ int launch_gqa_attn(int dt, const Batch& b, const GqaDims& D, const void* qn, co
 // 16-byte aligned.  When every sequence brings one token the key range can be cut over `splits` CTAs; that needs a workspace of
 // gqa_attn_mma_workspace(n * H, splits, dv) bytes.
 bool gqa_attn_mma_usable(const GqaDims& D, const PagedCache& pc);
+bool gqa_attn_mma_takes(const GqaDims& D);      // the score and mask options of D that the tensor-core form implements
 size_t gqa_attn_mma_workspace(int rows, int splits, int dv);
 int launch_gqa_attn_mma(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, float* workspace, int splits,
                         cudaStream_t s);
 
 // ---- gated delta rule ----------------------------------------------------------------------------------------------------
-struct DeltaDims { int H, Hk, d, dv; };
+// vec_decay: the decay has one entry per head and key channel ([n, H, d]) instead of one per head.  q_off / k_off / v_off: columns of the
+// first query head, key head and value head in a row (negative: the layout [q heads | k heads | v heads]).  no_delta: the write is
+// u = beta v (a plain decayed outer-product accumulation: the state-space recurrence) instead of u = beta (v - S^T k).
+struct DeltaDims { int H, Hk, d, dv; int vec_decay = 0, no_delta = 0, q_off = -1, k_off = -1, v_off = -1; };
 // in place on qkv float [n, C = 2 * Hk * d + H * dv] (ld): q and k heads -> unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.
-// beta[n, H] = sigmoid(b_raw), decay[n, H] = exp(-exp(A_log[h]) * softplus(a_raw + dt_bias[h]))   (a_raw, b_raw float with strides)
+// beta[n, H] = sigmoid(b_raw), decay[n, H] = exp(-exp(A_log[h]) * softplus(a_raw + dt_bias[h]))   (a_raw, b_raw float with strides);
+// with D.vec_decay a_raw and dt_bias have H * d entries and decay is [n, H, d]
 int launch_delta_prep(int dt, const DeltaDims& D, int n, float* qkv, int ld, const float* a_raw, int lda, const float* b_raw, int ldb_,
                       const void* A_log, const void* dt_bias, float* beta, float* decay, cudaStream_t s);
 // per (sequence, head): for each token in order  S = decay S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q.   S float [slot][H][d][dv]
 int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
                       size_t slot_stride, float* o, cudaStream_t s);
-// y T [n, H * dv] = o / sqrt(mean_dv(o^2) + eps) * w[dv] * silu(g float [n, H * dv] (ldg))
-int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s);
+// y T [n, H * dv] = o / sqrt(mean_dv(o^2) + eps) * w[dv] * act(g float [n, H * dv] (ldg)); act 0 silu, 1 sigmoid
+int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s, int act = 0);
+// state-space recurrence around launch_delta_rule (no_delta form).  prep: step[n, H] = softplus(dt_raw + dt_bias[h]) (no clamp),
+// decay[n, H] = exp(-exp(A_log[h]) * step).  post: y T [n, H * dv] = grouped RMS norm (groups equal parts of H * dv, weight w [H * dv]) of
+// (o + D[h] * x) * silu(z); x float [n, H * dv] (ldx), z float (ldz).
+int launch_ssd_prep(int dt, int n, int H, const float* dt_raw, int ld, const void* A_log, const void* dt_bias, float* step, float* decay, cudaStream_t s);
+int launch_ssd_post(int dt, int n, int H, int dv, int groups, const float* o, const float* x, int ldx, const float* z, int ldz, const void* Dskip,
+                    const void* w, float eps, void* y, cudaStream_t s);
 
 // ---- routed feed-forward ---------------------------------------------------------------------------------------------------
 struct RouterDims {
@@ -157,7 +184,7 @@ int launch_router_fused(int dt, const RouterDims& R, int n, const float* x, int 
 int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_t* counts, int32_t* scratch, int32_t* sorted_rows,
                     int32_t* pair_row, int32_t* tile_group, int P, cudaStream_t s);
 // hmid T [P, ff] = act(gu[:, :ff], gu[:, ff:])   (gu float [P, 2 ff]); rows of skipped tiles are left alone (tile_group null: every row).
-// act 0: silu(g) * u;  act 1: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(1.702 g) * (u + 1)
+// act 0: silu(g) * u;  act 1: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(1.702 g) * (u + 1);  act 2: gelu(g) * u (tanh form)
 int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s, int act = 0, float limit = 0.f);
 // out float [n, W] = sum_k wts[t, k] * (ids[t, k] < E ? y[pair_row[t, k], :] : h[t, :])     (h T [n, W]; pair_row null: row t * top + k)
 // shared_y (optional, float [n, W]): a shared expert's output, added times sigmoid(shared_gate[i * ld_gate]) (shared_gate null: times 1)

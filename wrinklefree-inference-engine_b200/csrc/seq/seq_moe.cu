@@ -208,6 +208,9 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int3
             if (act == 1) {
                 const float gg = fminf(g[v], limit), uu = fminf(fmaxf(u[v], -limit), limit);
                 a = gg * sigmoid_f(1.702f * gg) * (uu + 1.f);
+            } else if (act == 2) {
+                const float z = g[v];
+                a = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))) * u[v];
             } else a = silu_f(g[v]) * u[v];
             hmid[(size_t)r * ff + c + v] = from_f<T>(a);
         }

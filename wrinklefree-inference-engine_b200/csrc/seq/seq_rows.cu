@@ -5,17 +5,32 @@ namespace wf {
 namespace seq {
 
 template <typename T>
-__global__ void embed_f32_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens, int W, float* __restrict__ x) {
+__global__ void embed_f32_kernel(const T* __restrict__ table, const int32_t* __restrict__ tokens, int W, float* __restrict__ x, float scale, T* __restrict__ x_t) {
     const int i = blockIdx.x;
     const T* row = table + (size_t)tokens[i] * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) x[(size_t)i * W + c] = to_f(row[c]);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = to_f(row[c]) * scale;
+        x[(size_t)i * W + c] = v;
+        if (x_t) x_t[(size_t)i * W + c] = from_f<T>(v);
+    }
 }
 
-int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, int W, float* x, cudaStream_t s) {
+int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, int W, float* x, cudaStream_t s, float scale, void* x_t) {
     if (n <= 0) return WF_OK;
-    if (dt == WF_BF16) embed_f32_kernel<<<n, 256, 0, s>>>((const __nv_bfloat16*)table, tokens, W, x);
-    else embed_f32_kernel<<<n, 256, 0, s>>>((const float*)table, tokens, W, x);
+    if (dt == WF_BF16) embed_f32_kernel<<<n, 256, 0, s>>>((const __nv_bfloat16*)table, tokens, W, x, scale, (__nv_bfloat16*)x_t);
+    else embed_f32_kernel<<<n, 256, 0, s>>>((const float*)table, tokens, W, x, scale, (float*)x_t);
     return launch_check(cudaGetLastError(), "embed_f32");
+}
+
+__global__ void axpby_kernel(float* __restrict__ y, float a, const float* __restrict__ y2, float b, size_t count) {
+    for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < count; k += (size_t)gridDim.x * blockDim.x) y[k] = a * y[k] + b * y2[k];
+}
+
+int launch_axpby(float* y, float a, const float* y2, float b, size_t count, cudaStream_t s) {
+    if (count == 0) return WF_OK;
+    const int blocks = (int)((count + 255) / 256 > 4096 ? 4096 : (count + 255) / 256);
+    axpby_kernel<<<blocks, 256, 0, s>>>(y, a, y2, b, count);
+    return launch_check(cudaGetLastError(), "axpby");
 }
 
 // x[i, :] = table[tokens[i], :] + position vector of tok_pos[i]: entry 2k = sin(a), entry 2k + 1 = cos(a), a = pos * base^(-2k / W).
@@ -155,7 +170,7 @@ int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int gro
 template <typename T>
 __global__ void causal_taps_kernel(Batch b, const float* __restrict__ in, int ld_in, const T* __restrict__ w, int taps, int C,
                                    const float* __restrict__ state, size_t slot_stride, int identity, int silu, T* __restrict__ out_t, int ld_t,
-                                   float* __restrict__ out_f, int ld_f) {
+                                   float* __restrict__ out_f, int ld_f, const T* __restrict__ bias) {
     const int i = blockIdx.x;
     const int sq = b.tok_seq[i];
     const int li = i - b.seq_start[sq];                    // index inside this step's portion
@@ -167,6 +182,7 @@ __global__ void causal_taps_kernel(Batch b, const float* __restrict__ in, int ld
             const float v = src >= 0 ? in[(size_t)(i - li + src) * ld_in + c] : st[(size_t)(src + taps - 1) * C + c];
             acc = fmaf(to_f(w[(size_t)c * taps + j]), v, acc);
         }
+        if (bias) acc += to_f(bias[c]);
         if (silu) acc = silu_f(acc);
         if (out_t) out_t[(size_t)i * ld_t + c] = from_f<T>(acc);
         if (out_f) out_f[(size_t)i * ld_f + c] = acc;
@@ -174,12 +190,12 @@ __global__ void causal_taps_kernel(Batch b, const float* __restrict__ in, int ld
 }
 
 int launch_causal_taps(int dt, const Batch& b, const float* in, int ld_in, const void* w, int taps, int C, const float* state,
-                       size_t slot_stride, int identity, int silu, void* out_t, int ld_t, float* out_f, int ld_f, cudaStream_t s) {
+                       size_t slot_stride, int identity, int silu, void* out_t, int ld_t, float* out_f, int ld_f, cudaStream_t s, const void* bias) {
     if (b.n <= 0) return WF_OK;
     if (taps < 1) { set_error("causal_taps: taps %d", taps); return WF_ERR_INVALID; }
     dim3 grid(b.n, (C + 255) / 256 > 8 ? 8 : (C + 255) / 256);
-    if (dt == WF_BF16) causal_taps_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, (const __nv_bfloat16*)w, taps, C, state, slot_stride, identity, silu, (__nv_bfloat16*)out_t, ld_t, out_f, ld_f);
-    else causal_taps_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, (const float*)w, taps, C, state, slot_stride, identity, silu, (float*)out_t, ld_t, out_f, ld_f);
+    if (dt == WF_BF16) causal_taps_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, (const __nv_bfloat16*)w, taps, C, state, slot_stride, identity, silu, (__nv_bfloat16*)out_t, ld_t, out_f, ld_f, (const __nv_bfloat16*)bias);
+    else causal_taps_kernel<<<grid, 256, 0, s>>>(b, in, ld_in, (const float*)w, taps, C, state, slot_stride, identity, silu, (float*)out_t, ld_t, out_f, ld_f, (const float*)bias);
     return launch_check(cudaGetLastError(), "causal_taps");
 }
 

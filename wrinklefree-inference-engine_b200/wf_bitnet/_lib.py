@@ -112,10 +112,11 @@ _lib = None
 # ---- libwf_seq.so (include/wf_seq.h): the engine for layer-stack sequence models ------------------------------------------------
 SEQ_LIB_PATH = Path(os.environ.get("WF_SEQ_LIB", _PKG_ROOT / "libwf_seq.so"))
 WF_SEQ_F32, WF_SEQ_BF16 = 0, 1
-WF_SEQ_LATENT_ATTENTION, WF_SEQ_DELTA, WF_SEQ_GQA_ATTENTION = 0, 1, 2
+WF_SEQ_LATENT_ATTENTION, WF_SEQ_DELTA, WF_SEQ_GQA_ATTENTION, WF_SEQ_SSD = 0, 1, 2, 3
 WF_SEQ_BLOCK_SANDWICH, WF_SEQ_BLOCK_POST = 0, 1
 WF_SEQ_FF_NONE, WF_SEQ_FF_ROUTED, WF_SEQ_FF_DENSE = 0, 1, 2
-WF_SEQ_ACT_SILU, WF_SEQ_ACT_CLAMPED = 0, 1
+WF_SEQ_ACT_SILU, WF_SEQ_ACT_CLAMPED, WF_SEQ_ACT_GELU_TANH = 0, 1, 2
+WF_SEQ_QKNORM_NONE, WF_SEQ_QKNORM_UNIT, WF_SEQ_QKNORM_HEAD, WF_SEQ_QKNORM_FULL = 0, 1, 2, 3
 
 
 class SeqLayer(C.Structure):
@@ -130,6 +131,12 @@ class SeqLayer(C.Structure):
         ("dist_exp", C.c_float),
         ("ff_act", C.c_int), ("ff_limit", C.c_float), ("router_act", C.c_int), ("group_top", C.c_int), ("router_norm", C.c_int),
         ("router_scale", C.c_float), ("shared_ff", C.c_int), ("shared_limit", C.c_float),
+        ("rope_interleaved", C.c_int), ("chunk", C.c_int), ("rel_rows", C.c_int), ("sink", C.c_int),
+        ("softcap", C.c_float), ("rel_far", C.c_float),
+        ("decay_channels", C.c_int), ("decay_rank", C.c_int), ("gate_rank", C.c_int), ("gate_act", C.c_int),
+        ("out_norm_groups", C.c_int),
+        ("pair", C.c_int), ("mix_scale", C.c_float), ("pair_scale", C.c_float),
+        ("tied", C.c_int), ("tied_to", C.c_int),
     ]
 
     def __init__(self, *a, **kw):
@@ -146,6 +153,7 @@ class SeqConfig(C.Structure):
         ("norm_groups", C.c_int), ("canon_taps", C.c_int), ("page_size", C.c_int), ("max_pages", C.c_int), ("slots", C.c_int),
         ("max_step_tokens", C.c_int),
         ("block_form", C.c_int), ("residual_mult", C.c_float), ("pos_embed", C.c_int), ("pos_base", C.c_float),
+        ("n_extra", C.c_int), ("embed_scale", C.c_float), ("norm_weights", C.c_int), ("tied_head", C.c_int),
     ]
 
 

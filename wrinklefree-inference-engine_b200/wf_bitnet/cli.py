@@ -87,7 +87,7 @@ def main(argv=None) -> int:
         p.add_argument("--max-tokens", type=int, default=0 if name == "generate" else 4096, help="cache pool size in tokens")
         p.add_argument("--slots", type=int, default=4, help="sequences alive at once")
         p.add_argument("--page-size", type=int, default=16)
-        p.add_argument("--max-step-tokens", type=int, default=1024)
+        p.add_argument("--max-step-tokens", type=int, default=1024 if name == "generate" else 4096, help="most tokens in one engine step (larger batches are cut)")
         if name == "generate":
             p.add_argument("--prompt-ids", action="append", required=True, help="comma-separated token ids; repeat for several requests")
             p.add_argument("--max-new-tokens", type=int, default=16)

@@ -17,6 +17,8 @@ _MODULES: Dict[str, str] = {
     "KarusunForCausalLM": "sglang.srt.models.karusun",
     "Tutizen": "sglang.srt.models.tutizen",
     "TutizenForCausalLM": "sglang.srt.models.tutizen",
+    "Nukezen": "sglang.srt.models.nukezen",
+    "NukezenForCausalLM": "sglang.srt.models.nukezen",
 }
 
 

@@ -14,10 +14,12 @@ from .seq_engine import SeqEngine
 
 class SeqCausalLM:
     """Owns a native engine sized for `max_tokens` cached tokens and `slots` live sequences.  Subclasses implement
-    `read_config(config_dict)` -> object with vocab, width, eps, layers, `native_layers()` and `fill_native(SeqConfig)`."""
+    `read_config(config_dict)` -> object with vocab, width, eps, layers, `native_layers()` (one descriptor per layer; the descriptors of
+    second mixers that layers name through `pair` follow them) and `fill_native(SeqConfig)`."""
 
     architecture_names: Tuple[str, ...] = ()
     min_page_size = 1
+    reads_shapes = False       # True: read_config(config, shapes) also gets the checkpoint's tensor shapes (sizes that config.json leaves to them)
 
     @staticmethod
     def read_config(config: Dict):
@@ -28,10 +30,10 @@ class SeqCausalLM:
         return False
 
     def __init__(self, config: Dict, *, dtype: str = "bfloat16", max_tokens: int = 4096, slots: int = 4, page_size: int = 16,
-                 max_step_tokens: int = 1024, build: bool = False):
+                 max_step_tokens: int = 1024, build: bool = False, shapes: Dict[str, tuple] = None):
         if dtype not in ("bfloat16", "float32"):
             raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
-        self.config = self.read_config(config)
+        self.config = self.read_config(config, shapes) if self.reads_shapes else self.read_config(config)
         c = self.config
         self.dtype = dtype
         self.page_size = page_size
@@ -42,8 +44,10 @@ class SeqCausalLM:
         nc.norm_groups, nc.canon_taps = 1, 1
         nc.page_size, nc.max_pages, nc.slots, nc.max_step_tokens = page_size, pages, slots, max_step_tokens
         c.fill_native(nc)
+        layers = c.native_layers()                   # one descriptor per layer, then the second mixers of paired layers
+        nc.n_extra = len(layers) - nc.n_layers
         self.native_config = nc
-        self.engine = SeqEngine(nc, c.native_layers(), build=build)
+        self.engine = SeqEngine(nc, layers, build=build)
         self.vocab = c.vocab
         self.max_step_tokens = max_step_tokens
 
@@ -53,6 +57,12 @@ class SeqCausalLM:
         max_step_tokens, build."""
         from pathlib import Path
         cfg = config if config is not None else checkpoint.read_config(model_dir)
+        if cls.reads_shapes and "shapes" not in serving:
+            f = checkpoint.SafetensorsFile(Path(model_dir) / "model.safetensors")
+            try:
+                serving["shapes"] = {n: f.info(n)[1] for n in f.names()}
+            finally:
+                f.close()
         m = cls(cfg, **serving)
         m.load_safetensors(Path(model_dir) / "model.safetensors")
         return m
