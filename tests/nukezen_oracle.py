@@ -191,3 +191,67 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens, streams: Option
             streams.append(x.clone())
     x = rms_unit(x, eps) * w["final.norm"]
     return x @ w["embed"].T
+
+
+def random_weights(cfg: Dict, seed: int = 0, sizes: Optional[Dict[int, Dict[str, int]]] = None) -> Dict[str, torch.Tensor]:
+    """Random tensors with the checkpoint's names and shapes, values representable in bfloat16.  `sizes[layer]` gives what config.json
+    leaves to the tensor shapes: 'rank_a' / 'rank_g' (two-matrix projections of a 'channel_delta' layer) and 'rel_rows' (bias table of an
+    'attention' layer)."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+    out: Dict[str, torch.Tensor] = {}
+    sizes = sizes or {}
+
+    def mat(name, o, i, s=None):
+        out[name] = (torch.randn(o, i, generator=g) * (s if s is not None else 1.0 / math.sqrt(i))).bfloat16().float()
+
+    def vec(name, n, s=0.1, mean=0.0):
+        out[name] = (mean + torch.randn(n, generator=g) * s).bfloat16().float()
+
+    out["embed"] = (torch.randn(V, W, generator=g) * 0.5).bfloat16().float()
+    vec("final.norm", W, 0.1, 1.0)
+    for li, L in enumerate(cfg["layers"]):
+        if L.get("weights_of") is not None:
+            continue
+        p, m, sz = f"l{li}.", L["mixer"], sizes.get(li, {})
+        vec(p + "norm1", W, 0.1, 1.0)
+        if L["type"] == "parallel":
+            a, q = m["left"], p + "mix.left."
+            H, G, d, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            mat(q + "q", H * d, W); vec(q + "q.b", H * d)
+            mat(q + "k", G * d, W); vec(q + "k.b", G * d)
+            mat(q + "v", G * dv, W); vec(q + "v.b", G * dv)
+            vec(q + "q.norm", d, 0.2, 1.0); vec(q + "k.norm", d, 0.2, 1.0)
+            mat(q + "g", H * dv, W); mat(q + "o", W, H * dv)
+            r, q = m["right"], p + "mix.right."
+            H, P, N, Gr = r["heads"], r["vdim"], r["state"], r["groups"]
+            C = H * P + 2 * Gr * N
+            mat(q + "in", 2 * H * P + 2 * Gr * N + H, W)
+            mat(q + "conv", C, r["conv"], 0.5); vec(q + "conv.b", C)
+            vec(q + "dt_bias", H, 0.5); vec(q + "A_log", H, 0.5); vec(q + "D", H, 0.5)
+            vec(q + "norm", H * P, 0.1, 1.0); mat(q + "o", W, H * P)
+        elif L["type"] == "channel_delta":
+            q = p + "mix."
+            H, Hk, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            ra, rg = sz.get("rank_a", 5), sz.get("rank_g", 6)
+            for nm, rows in (("q", Hk * d), ("k", Hk * d), ("v", H * dv)):
+                mat(q + nm, rows, W); mat(q + nm + ".conv", rows, m["conv"], 0.5)
+            mat(q + "b", H, W)
+            vec(q + "A_log", H, 0.5); vec(q + "norm", dv, 0.1, 1.0)
+            mat(q + "a1", ra, W); mat(q + "a2", H * d, ra, 1.0); vec(q + "dt_bias", H * d, 0.5)
+            mat(q + "g1", rg, W); mat(q + "g2", H * dv, rg, 1.0)
+            mat(q + "o", W, H * dv)
+        elif L["type"] == "attention":
+            q = p + "mix."
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            mat(q + "q", H * d, W); mat(q + "k", G * d, W); mat(q + "v", G * dv, W)
+            vec(q + "q.norm", H * d, 0.2, 1.0); vec(q + "k.norm", G * d, 0.2, 1.0)
+            mat(q + "rel", sz.get("rel_rows", 8), H, 1.0)
+            mat(q + "o", W, H * dv)
+        else:
+            raise ValueError(L["type"])
+        f = L.get("mlp")
+        if f is not None:
+            vec(p + "norm2", W, 0.1, 1.0)
+            mat(p + "mlp.gate", f["ff"], W); mat(p + "mlp.up", f["ff"], W); mat(p + "mlp.down", W, f["ff"])
+    return out

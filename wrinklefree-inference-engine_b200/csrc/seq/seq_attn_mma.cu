@@ -55,7 +55,9 @@ struct AmParams {
 };
 
 // DKP / DVP: per-head key and value sizes rounded up to 64 or 128.  DECODE: the decode form.  NSTAGE: staged tiles (ring depth).
-template <int DKP, int DVP, bool DECODE, int NSTAGE>
+// EXT: the score of an element is formed in full (scale, tanh cap, bias by distance, distance penalty) instead of by the one-FMA form
+// that scale and penalty alone allow.
+template <int DKP, int DVP, bool DECODE, int NSTAGE, bool EXT>
 __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, GqaDims D, const __nv_bfloat16* __restrict__ qn, const float* __restrict__ gate,
                                                                     PagedCache pc, __nv_bfloat16* __restrict__ out, AmParams ap) {
     constexpr int KS = DKP + 8, VS = DVP + 8;              // shared-memory row strides in elements
@@ -87,7 +89,7 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
     const int32_t* bt = pc.block_table + (size_t)b.seq_slot[sq] * pc.max_blocks;
     // rows of this warp: row r (0..15) of the warp's 16 -> token (row_base + r) >> rp2_log, head-in-group (row_base + r) & (rp2 - 1)
     const int row_base = DECODE ? 0 : warp * 16;
-    int r_tok[2], r_head[2], r_pos[2];
+    int r_tok[2], r_head[2], r_pos[2], r_lo[2];          // r_lo: the first key the row sees (window and chunk)
     bool r_ok[2];
     float r_slope2[2];                                     // slope of the row's head times log2 e
 #pragma unroll
@@ -95,13 +97,18 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
         const int r = row_base + g4 + 8 * k;
         const int tk = r >> ap.rp2_log, hg = r & (ap.rp2 - 1);
         r_ok[k] = tk < ntok && hg < rep;
-        r_tok[k] = flat0 + tk; r_head[k] = kvh * rep + hg; r_pos[k] = pos0 + tk;
+        r_tok[k] = flat0 + tk; r_head[k] = kvh * rep + (hg < rep ? hg : 0); r_pos[k] = pos0 + tk;
+        r_lo[k] = r_pos[k] - D.window + 1;
+        if (D.chunk > 0) { const int c0 = r_pos[k] / D.chunk * D.chunk; if (c0 > r_lo[k]) r_lo[k] = c0; }
         r_slope2[k] = D.dist_exp > 0.f ? exp2f(-D.dist_exp * (float)(r_head[k] + 1) / (float)D.H) * LOG2E : 0.f;
     }
     const float scale2 = D.scale * LOG2E;
     // first and last position among the rows of this warp that exist
     const int wpos_min = pos0 + (row_base >> ap.rp2_log);
     const int wpos_max = pos0 + ((row_base + 15) >> ap.rp2_log) < pos_last ? pos0 + ((row_base + 15) >> ap.rp2_log) : pos_last;
+    // the latest "first visible key" among them (both bounds grow with the position)
+    int wlo_max = wpos_max - D.window + 1;
+    if (D.chunk > 0) { const int c0 = wpos_max / D.chunk * D.chunk; if (c0 > wlo_max) wlo_max = c0; }
     // query fragments (A operand), zero beyond d and for rows that do not exist
     uint32_t qf[NKS][4];
 #pragma unroll
@@ -116,7 +123,8 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
                 qf[ks][k + 2 * hlf] = v;
             }
     // key range of the tile: every key some row of the tile may see, cut into AM_KT-key tiles aligned to multiples of AM_KT
-    const int lo_all = pos0 - D.window + 1 > 0 ? pos0 - D.window + 1 : 0;
+    int lo_all = pos0 - D.window + 1 > 0 ? pos0 - D.window + 1 : 0;
+    if (D.chunk > 0) { const int c0 = pos0 / D.chunk * D.chunk; if (c0 > lo_all) lo_all = c0; }
     int t_lo = lo_all / AM_KT, t_hi = pos_last / AM_KT;    // inclusive
     if (DECODE && ap.splits > 1) {
         const int nt = t_hi - t_lo + 1, per = (nt + ap.splits - 1) / ap.splits;
@@ -209,8 +217,23 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
         for (int k = 0; k < 2; ++k) nb[k] = -r_slope2[k] * (float)(r_pos[k] - jt0 - 2 * t4);
         float mx[2] = {-INFINITY, -INFINITY};
         // a tile every row of the warp sees whole needs no mask: its last key is not after the warp's first position, its first not before the window
-        const bool whole = jt0 + KW - 1 <= wpos_min && jt0 > wpos_max - D.window;
-        if (whole) {
+        const bool whole = jt0 + KW - 1 <= wpos_min && jt0 >= wlo_max;
+        if (EXT) {
+#pragma unroll
+            for (int j = 0; j < NST; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int k = e >> 1, key = jt0 + j * 8 + 2 * t4 + (e & 1);
+                    const int dist = r_pos[k] - key;
+                    const bool vis = whole || (r_ok[k] && dist >= 0 && key >= r_lo[k]);
+                    float v = s[j][e] * D.scale;
+                    if (D.softcap > 0.f) v = D.softcap * tanhf(v / D.softcap);
+                    if (D.rel) { const int dd = dist < 0 ? 0 : (dist < D.rel_n ? dist : D.rel_n - 1); v += __ldg(D.rel + (size_t)dd * D.H + r_head[k]); }
+                    v = vis ? fmaf(v, LOG2E, -r_slope2[k] * (float)dist) : -INFINITY;
+                    s[j][e] = v;
+                    mx[k] = fmaxf(mx[k], v);
+                }
+        } else if (whole) {
 #pragma unroll
             for (int j = 0; j < NST; ++j)
 #pragma unroll
@@ -227,7 +250,7 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
                 for (int e = 0; e < 4; ++e) {
                     const int k = e >> 1, key = jt0 + j * 8 + 2 * t4 + (e & 1);
                     const int dist = r_pos[k] - key;
-                    const bool vis = r_ok[k] && dist >= 0 && dist < D.window;
+                    const bool vis = r_ok[k] && dist >= 0 && key >= r_lo[k];
                     const float v = vis ? fmaf(s[j][e], scale2, fmaf(r_slope2[k], (float)(j * 8 + (e & 1)), nb[k])) : -INFINITY;
                     s[j][e] = v;
                     mx[k] = fmaxf(mx[k], v);
@@ -294,12 +317,14 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             if (!r_ok[k]) continue;
-            const float mul = (gate ? gate[(size_t)r_tok[k] * D.H + r_head[k]] : 1.f) / l_run[k];
+            const float lsum = D.sink ? l_run[k] + exp2f(-m_run[k]) : l_run[k];      // the extra key: score 0, no value
+            const float mul = (gate && !D.gate_elem ? gate[(size_t)r_tok[k] * D.H + r_head[k]] : 1.f) / lsum;
             __nv_bfloat16* dst = out + ((size_t)r_tok[k] * D.H + r_head[k]) * D.dv;
+            const float* ge = gate && D.gate_elem ? gate + ((size_t)r_tok[k] * D.H + r_head[k]) * D.dv : nullptr;
 #pragma unroll
             for (int j = 0; j < NVT; ++j) {
                 const int c = j * 8 + 2 * t4;
-                if (c < D.dv) *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(o[j][2 * k] * mul, o[j][2 * k + 1] * mul);
+                if (c < D.dv) *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(o[j][2 * k] * mul * (ge ? ge[c] : 1.f), o[j][2 * k + 1] * mul * (ge ? ge[c + 1] : 1.f));
             }
         }
         return;
@@ -340,19 +365,22 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
             }
             if (lane == 0) { dst[D.dv] = mg; dst[D.dv + 1] = lg; }
         } else {
-            const float mul = (gate ? gate[(size_t)tok * D.H + head] : 1.f) / lg;
+            if (D.sink) lg += exp2f(-mg);
+            const float mul = (gate && !D.gate_elem ? gate[(size_t)tok * D.H + head] : 1.f) / lg;
+            const float* ge = gate && D.gate_elem ? gate + ((size_t)tok * D.H + head) * D.dv : nullptr;
             for (int c = lane; c < D.dv; c += 32) {
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) v += sm_o[((size_t)w * 16 + r) * DVP + c] * sc[w];
-                out[((size_t)tok * D.H + head) * D.dv + c] = __float2bfloat16_rn(v * mul);
+                out[((size_t)tok * D.H + head) * D.dv + c] = __float2bfloat16_rn(v * mul * (ge ? ge[c] : 1.f));
             }
         }
     }
 }
 
 // one warp per (token, head): merge the key splits' partial results (maxima in units of log 2), apply the gate
-__global__ void gqa_attn_merge_kernel(int rows, int splits, int dv, const float* __restrict__ part, const float* __restrict__ gate, __nv_bfloat16* __restrict__ out) {
+__global__ void gqa_attn_merge_kernel(int rows, int splits, int dv, const float* __restrict__ part, const float* __restrict__ gate, __nv_bfloat16* __restrict__ out,
+                                      int sink, int gate_elem) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     const float* p = part + (size_t)row * splits * (dv + 2);
@@ -360,36 +388,43 @@ __global__ void gqa_attn_merge_kernel(int rows, int splits, int dv, const float*
     for (int z = 0; z < splits; ++z) mg = fmaxf(mg, p[(size_t)z * (dv + 2) + dv]);
     float lg = 0.f;
     for (int z = 0; z < splits; ++z) { const float m = p[(size_t)z * (dv + 2) + dv]; lg += m == -INFINITY ? 0.f : p[(size_t)z * (dv + 2) + dv + 1] * exp2f(m - mg); }
-    const float mul = (gate ? gate[row] : 1.f) / lg;
+    if (sink) lg += exp2f(-mg);
+    const float mul = (gate && !gate_elem ? gate[row] : 1.f) / lg;
     for (int c = lane; c < dv; c += 32) {
         float v = 0.f;
         for (int z = 0; z < splits; ++z) { const float m = p[(size_t)z * (dv + 2) + dv]; if (m != -INFINITY) v += p[(size_t)z * (dv + 2) + c] * exp2f(m - mg); }
-        out[(size_t)row * dv + c] = __float2bfloat16_rn(v * mul);
+        out[(size_t)row * dv + c] = __float2bfloat16_rn(v * mul * (gate && gate_elem ? gate[(size_t)row * dv + c] : 1.f));
     }
 }
 
-template <int DKP, int DVP, bool DECODE, int NSTAGE>
+template <int DKP, int DVP, bool DECODE, int NSTAGE, bool EXT>
 int am_launch(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, const AmParams& ap, int tiles, cudaStream_t s) {
     size_t smem = (size_t)NSTAGE * AM_KT * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(128 + 64 * DVP) * sizeof(float);
     if (DECODE && merge > smem) smem = merge;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cuda_check(cudaFuncSetAttribute(gqa_attn_mma_kernel<DKP, DVP, DECODE, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attention shared memory")) return WF_ERR_CUDA;
+        if (cuda_check(cudaFuncSetAttribute(gqa_attn_mma_kernel<DKP, DVP, DECODE, NSTAGE, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attention shared memory")) return WF_ERR_CUDA;
         attr_set = true;
     }
     dim3 grid(tiles, D.G, DECODE ? ap.splits : 1);
-    gqa_attn_mma_kernel<DKP, DVP, DECODE, NSTAGE><<<grid, AM_THREADS, smem, s>>>(b, D, (const __nv_bfloat16*)qn, gate, pc, (__nv_bfloat16*)out, ap);
+    gqa_attn_mma_kernel<DKP, DVP, DECODE, NSTAGE, EXT><<<grid, AM_THREADS, smem, s>>>(b, D, (const __nv_bfloat16*)qn, gate, pc, (__nv_bfloat16*)out, ap);
     return launch_check(cudaGetLastError(), "gqa_attn_mma");
 }
 
 template <bool DECODE, int NSTAGE>
 int am_dispatch(const Batch& b, const GqaDims& D, const void* qn, const float* gate, const PagedCache& pc, void* out, const AmParams& ap, int tiles, cudaStream_t s) {
     const bool k64 = D.d <= 64, v64 = D.dv <= 64;
-    if (k64 && v64) return am_launch<64, 64, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
-    if (k64) return am_launch<64, 128, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
-    if (v64) return am_launch<128, 64, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
-    return am_launch<128, 128, DECODE, NSTAGE>(b, D, qn, gate, pc, out, ap, tiles, s);
+    if (D.softcap > 0.f || D.rel) {
+        if (k64 && v64) return am_launch<64, 64, DECODE, NSTAGE, true>(b, D, qn, gate, pc, out, ap, tiles, s);
+        if (k64) return am_launch<64, 128, DECODE, NSTAGE, true>(b, D, qn, gate, pc, out, ap, tiles, s);
+        if (v64) return am_launch<128, 64, DECODE, NSTAGE, true>(b, D, qn, gate, pc, out, ap, tiles, s);
+        return am_launch<128, 128, DECODE, NSTAGE, true>(b, D, qn, gate, pc, out, ap, tiles, s);
+    }
+    if (k64 && v64) return am_launch<64, 64, DECODE, NSTAGE, false>(b, D, qn, gate, pc, out, ap, tiles, s);
+    if (k64) return am_launch<64, 128, DECODE, NSTAGE, false>(b, D, qn, gate, pc, out, ap, tiles, s);
+    if (v64) return am_launch<128, 64, DECODE, NSTAGE, false>(b, D, qn, gate, pc, out, ap, tiles, s);
+    return am_launch<128, 128, DECODE, NSTAGE, false>(b, D, qn, gate, pc, out, ap, tiles, s);
 }
 
 int g_decode_stages = -1;
@@ -402,7 +437,7 @@ bool gqa_attn_mma_usable(const GqaDims& D, const PagedCache& pc) {
            ((long long)pc.page_size * D.d) % 8 == 0 && D.G <= 65535;
 }
 
-bool gqa_attn_mma_takes(const GqaDims& D) { return D.chunk == 0 && D.softcap == 0.f && !D.rel && !D.sink && !D.gate_elem; }
+bool gqa_attn_mma_takes(const GqaDims& D) { return D.chunk >= 0 && D.softcap >= 0.f; }
 
 size_t gqa_attn_mma_workspace(int rows, int splits, int dv) { return (size_t)rows * splits * (dv + 2) * sizeof(float); }
 
@@ -427,7 +462,7 @@ int launch_gqa_attn_mma(const Batch& b, const GqaDims& D, const void* qn, const 
                      : (g_decode_stages == 3 ? am_dispatch<true, 3>(b, D, qn, gate, pc, out, ap, tiles, s) : am_dispatch<true, 2>(b, D, qn, gate, pc, out, ap, tiles, s));
     if (rc || ap.splits == 1) return rc;
     const int rows = b.n * D.H;
-    gqa_attn_merge_kernel<<<(rows + 3) / 4, 128, 0, s>>>(rows, ap.splits, D.dv, workspace, gate, (__nv_bfloat16*)out);
+    gqa_attn_merge_kernel<<<(rows + 3) / 4, 128, 0, s>>>(rows, ap.splits, D.dv, workspace, gate, (__nv_bfloat16*)out, D.sink, D.gate_elem);
     return launch_check(cudaGetLastError(), "gqa_attn_merge");
 }
 

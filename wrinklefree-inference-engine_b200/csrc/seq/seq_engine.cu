@@ -423,7 +423,8 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
         // The cut depends on the batch size and the pool only, never on the lengths: a captured step stays valid.
         int splits = 1;
         if (n == b.nseq) {
-            const long long span = std::min<long long>(c.window, (long long)e->cfg.max_pages * e->cfg.page_size);
+            long long span = std::min<long long>(c.window, (long long)e->cfg.max_pages * e->cfg.page_size);
+            if (c.chunk > 0 && c.chunk < span) span = c.chunk;
             const int ctas = n * c.kv_heads, resident = 2 * sm_count();
             splits = (e->attn_waves * resident + ctas - 1) / ctas;
             if (splits > span / 256) splits = (int)(span / 256);
