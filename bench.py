@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """bench.py — decode throughput of the BitNet-2B-4T-shaped hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1|hybrid|tutizen]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1|hybrid|tutizen|nukezen]
 
 --workload hybrid (1 GPU) measures the layer-stack sequence engine (latent attention / gated delta rule / routed feed-forward) instead:
 prefill and decode tok/s at two layer sizes with random weights, per launch-group times, and the BitNet engine at equal size beside it.
@@ -794,9 +794,11 @@ def hybrid_config(z):
     return {"architecture": "Karusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4}, "canon": {"taps": 4}, "layers": layers}
 
 
-def hybrid_model(cfg, max_tokens, slots, max_step_tokens):
+def hybrid_model(cfg, max_tokens, slots, max_step_tokens, shapes=None):
     from wf_bitnet import registry
-    m = registry.resolve(cfg)(cfg, dtype="bfloat16", max_tokens=max_tokens, slots=slots, page_size=16, max_step_tokens=max_step_tokens)
+    cls = registry.resolve(cfg)
+    extra = {"shapes": shapes} if getattr(cls, "reads_shapes", False) else {}
+    m = cls(cfg, dtype="bfloat16", max_tokens=max_tokens, slots=slots, page_size=16, max_step_tokens=max_step_tokens, **extra)
     rng = np.random.default_rng(0)
     base = torch.from_numpy(rng.standard_normal(1 << 22).astype(np.float32)).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     for name, count, _ in m.engine.expected_tensors():
@@ -913,7 +915,7 @@ TUTIZEN_SIZES = {
 }
 
 
-def tutizen_config(z):
+def tutizen_config(z, all_dense=False):
     def att(src=None):
         m = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["d"], "vdim": z["dv"], "scale": z["d"] ** -0.5}
         if src is not None:
@@ -924,7 +926,7 @@ def tutizen_config(z):
     dense = {"kind": "dense", "ff": z["top"] * z["ff"], "limit": 7.0}
     layers = []
     for i in range(z["layers"]):            # pairs: a layer with its own keys / values, then one that reads them
-        layers.append(dict(att(None if i % 2 == 0 else i - 1), mlp=dense if i % 4 == 2 else moe))
+        layers.append(dict(att(None if i % 2 == 0 else i - 1), mlp=dense if (all_dense or i % 4 == 2) else moe))
     return {"architecture": "Tutizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": layers}
 
 
@@ -937,12 +939,12 @@ def karusun_attention_config(z):
             "layers": [dict(lat, mlp=ff) for _ in range(z["layers"])]}
 
 
-def measure_seq_model(cfg, prompt, decode_points, K):
+def measure_seq_model(cfg, prompt, decode_points, K, shapes=None):
     """prefill of one prompt from an empty cache and decode steps at (batch, context) points, CUDA-event times on the engine's stream
     (decode steps as graph replays), plus the per-launch-group profile of the prompt and of the smallest and largest decode point."""
     max_b = max(b for b, _ in decode_points)
     tokens_cap = max(max(b * (c + 16) for b, c in decode_points), prompt + 16)
-    m = hybrid_model(cfg, tokens_cap, max_b, prompt)
+    m = hybrid_model(cfg, tokens_cap, max_b, prompt, shapes)
     slots = [m.admit() for _ in range(max_b)]
     res, launches = {}, 0
     ms = m.engine.time_step(slots[:1], [prompt], iters=K)
@@ -996,6 +998,74 @@ def run_tutizen(args):
           "hbm_peak_gbs": peak, "peak_source": peak_src, "sizes": out, "clocks": clocks, "gpu_launches": launches})
     return 0
 
+# --workload nukezen: the Nukezen design (paired window attention + state-space mixers, a delta rule with per-channel decay, chunk-local
+# attention with capped scores, distance bias and a softmax sink; dense gelu units) on the sequence engine at sizes that resemble real
+# layers, random weights, beside the closest existing model on the same engine at equal width / heads / layers / feed-forward size:
+# Tutizen with dense units (grouped-query attention in the same block form).
+NUKEZEN_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, d=128, dv=128, window=1024, rot=64, chunk=8192, ssd_heads=16, ssd_p=64, ssd_n=64, ssd_groups=2,
+                  dl_heads=8, dl_kv=4, dl_d=64, dl_dv=128, rank=64, rel_rows=32, top=6, ff=384, vocab=32768, layers=4, experts=0, groups=1, keep=1),
+    "w2560": dict(width=2560, heads=20, kv_heads=5, d=128, dv=128, window=4096, rot=64, chunk=8192, ssd_heads=40, ssd_p=64, ssd_n=128, ssd_groups=5,
+                  dl_heads=20, dl_kv=10, dl_d=128, dl_dv=128, rank=128, rel_rows=32, top=6, ff=1152, vocab=128256, layers=4, experts=0, groups=1, keep=1),
+}
+
+
+def nukezen_config(z):
+    """-> (config, tensor shapes that carry the sizes config.json leaves to the checkpoint)"""
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["d"], "vdim": z["dv"], "scale": z["d"] ** -0.5, "mask": {"size": z["window"]},
+            "rot": {"dims": z["rot"], "base": 10000.0}}
+    right = {"heads": z["ssd_heads"], "vdim": z["ssd_p"], "state": z["ssd_n"], "groups": z["ssd_groups"], "conv": 4, "norm_groups": z["ssd_groups"]}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    par = {"type": "parallel", "mixer": {"left": left, "left_scale": 0.7, "right": right, "right_scale": 0.7}, "mlp": dense}
+    dl = {"type": "channel_delta", "mixer": {"heads": z["dl_heads"], "kv_heads": z["dl_kv"], "dim": z["dl_d"], "vdim": z["dl_dv"], "conv": 4}, "mlp": dense}
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["d"], "vdim": z["dv"], "scale": z["d"] ** -0.5, "softcap": 30.0,
+                                          "bias_max": z["chunk"], "mask": {"size": z["chunk"]}}, "mlp": dense}
+    layers, shapes = [], {}
+    for i in range(z["layers"]):
+        L = (par, dl, dict(par, weights_of=0), att)[i % 4]
+        layers.append(L)
+        if L["type"] == "channel_delta":
+            shapes[f"l{i}.mix.a1"] = (z["rank"], z["width"]); shapes[f"l{i}.mix.g1"] = (z["rank"], z["width"])
+        if L["type"] == "attention":
+            shapes[f"l{i}.mix.rel"] = (z["rel_rows"], z["heads"])
+    cfg = {"architecture": "Nukezen", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": layers}
+    return cfg, shapes
+
+
+def run_nukezen(args):
+    from wf_bitnet import _lib
+    torch.cuda.set_device(0)
+    _lib.require_gpu()
+    K, W_ = max(2, args.steps), max(3, args.warmup)
+    peak, peak_src = measured_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    out, launches = {}, 0
+    for name, z in NUKEZEN_SIZES.items():
+        if args.hybrid_size and name != args.hybrid_size:
+            continue
+        prompt = 2048
+        decode_points = [(1, 512), (8, 2048), (64, 4096)] if name == "w2560" else [(1, 512), (8, 1024), (64, 1024)]
+        cfg, shapes = nukezen_config(z)
+        res, n1 = measure_seq_model(cfg, prompt, decode_points, K, shapes)
+        res["layer_kinds"] = [L["type"] + (f" (weights of layer {L['weights_of']})" if "weights_of" in L else "") + " + dense" for L in cfg["layers"]]
+        # state one decoded token reads and writes per recurrent layer (float), cached keys and values per attention layer and 1000 tokens
+        res["state_bytes"] = {"state_space": 4 * z["ssd_heads"] * z["ssd_n"] * z["ssd_p"], "channel_delta": 4 * z["dl_heads"] * z["dl_d"] * z["dl_dv"]}
+        res["kv_bytes_per_layer_per_1k_ctx"] = 1000 * z["kv_heads"] * (z["d"] + z["dv"]) * 2
+        tres, n2 = measure_seq_model(tutizen_config(z, all_dense=True), prompt, decode_points, K)
+        res["tutizen_equal_size"] = tres
+        launches += n1 + n2
+        out[name] = res
+    clocks = sampler.stop()
+    head = out.get("w2560") or next(iter(out.values()))
+    top = sorted(head["decode"].items())[-1]
+    emit({"metric": "prefill / decode tok/s of the Nukezen design on the sequence engine beside Tutizen (dense units) at equal size", "workload": "nukezen",
+          "value": top[1]["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W_, "higher_is_better": True, "dtype": "bf16",
+          "data": "synthetic (random weights; decode contexts are whatever the cache pages hold)", "vs_baseline": None,
+          "config": {"model": "Nukezen-shaped, " + ", ".join(out), "point": top[0], "l2": "weights per step exceed L2 (126 MB) at w2560; w1024 is L2-resident"},
+          "hbm_peak_gbs": peak, "peak_source": peak_src, "sizes": out, "clocks": clocks, "gpu_launches": launches})
+    return 0
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -1003,17 +1073,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1", "hybrid", "tutizen"] + sorted(TP_WORKLOADS))
-    ap.add_argument("--hybrid-size", default="", help="--workload hybrid / tutizen: run only this size (w1024 | w2560)")
+    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1", "hybrid", "tutizen", "nukezen"] + sorted(TP_WORKLOADS))
+    ap.add_argument("--hybrid-size", default="", help="--workload hybrid / tutizen / nukezen: run only this size (w1024 | w2560)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the batch-1 aux measurement")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel suite (aux.tp)")
     args = ap.parse_args()
-    if args.workload in ("hybrid", "tutizen"):
+    if args.workload in ("hybrid", "tutizen", "nukezen"):
         if args.impl == "reference":
             emit({"impl": "reference", "unavailable": "the reference has no model of this design; its arm is defined for the 2B workloads only"})
             return 0
-        return run_hybrid(args) if args.workload == "hybrid" else run_tutizen(args)
+        return {"hybrid": run_hybrid, "tutizen": run_tutizen, "nukezen": run_nukezen}[args.workload](args)
     if args.workload in TP_WORKLOADS:
         if args.impl == "reference":
             emit({"impl": "reference", "unavailable": "the reference arm is defined for the 2B workloads (bs64 / bs1) only"})

@@ -445,7 +445,7 @@ def test_command_line_trace_replay_and_generate(tmp_path):
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parent.parent
-    cs = CONFIGS["odd"]
+    cs = CONFIGS["mixed"]
     cfg, w = cs[0], make_weights(cs, 151)
     _write_model_dir(tmp_path, cfg, w)
     reqs = {"a": tokens_for(cfg, 21, 152), "b": tokens_for(cfg, 9, 153), "c": tokens_for(cfg, 14, 154)}
@@ -469,9 +469,8 @@ def test_command_line_trace_replay_and_generate(tmp_path):
                            input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
         assert [ln for ln in r.stdout.splitlines() if ln.startswith("done ")] == [f"done {n}" for n in range(len(plan))]
-        for n, rows in enumerate(expect):
-            got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"])
-            assert_close(got, np.stack([want[rid][pos] for rid, pos in rows]), dtype, n, 1.5)
+        got = [np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"]) for n, rows in enumerate(expect)]
+        assert_close(np.concatenate(got), np.stack([want[rid][pos] for rows in expect for rid, pos in rows]), dtype, dtype, 1.5)
     r = subprocess.run([sys.executable, "-m", "wf_bitnet.cli", "generate", "--model", str(tmp_path), "--dtype", "float32", "--max-new-tokens", "5",
                         "--prompt-ids", ",".join(map(str, reqs["a"])), "--prompt-ids", ",".join(map(str, reqs["b"])), "--slots", "1", "--prefill-chunk", "4"],
                        capture_output=True, text=True, timeout=600, env=dict(__import__("os").environ, PYTHONPATH=str(root / "wrinklefree-inference-engine_b200")))

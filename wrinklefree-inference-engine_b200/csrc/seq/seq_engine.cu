@@ -451,13 +451,14 @@ int run_one_mixer(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     }
 }
 
-// h_t -> y.  A paired layer runs its two mixers one after the other on the same input (they share the projection workspaces) and
-// combines their outputs in float.
-int run_mixer(wf_seq_engine* e, LayerState& L, const Batch& b) {
+// h_t -> y.  A paired layer runs its two mixers one after the other on the same input (they share the projection workspaces); their
+// outputs are combined in float, here or (combine = false) by the norm kernel that follows.
+int run_mixer(wf_seq_engine* e, LayerState& L, const Batch& b, bool combine = true) {
     int rc;
     if ((rc = run_one_mixer(e, L, b, e->y))) return rc;
     if (!L.c.pair) return WF_OK;
     if ((rc = run_one_mixer(e, e->layers[L.pair_state], b, e->y2))) return rc;
+    if (!combine) return WF_OK;                  // the caller's norm kernel forms mix_scale * y + pair_scale * y2 on its way in
     rc = launch_axpby(e->y, L.c.mix_scale, e->y2, L.c.pair_scale, (size_t)b.n * e->cfg.width, e->stream);
     mark(e, "pair.combine");
     return rc;
@@ -584,8 +585,8 @@ int run_layers_post(wf_seq_engine* e, const StepView& v) {
     mark(e, "embed");
     for (int li = 0; li < e->cfg.n_layers; ++li) {
         LayerState& L = e->layers[li];
-        if ((rc = run_mixer(e, L, v.b))) return rc;
-        if (vec) rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm1, 1, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s);
+        if ((rc = run_mixer(e, L, v.b, !vec))) return rc;
+        if (vec) rc = launch_group_rmsnorm(e->dt, e->y, W, L.norm1, 1, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s, L.c.pair ? e->y2 : nullptr, L.c.mix_scale, L.c.pair_scale);
         else rc = launch_scalar_rmsnorm(e->dt, e->y, W, L.c.pair ? nullptr : L.ob, L.norm1, mult, eps, n, W, e->x, e->x, W, e->h_t, W, nullptr, s);
         if (rc) return rc;
         mark(e, "norm+residual");

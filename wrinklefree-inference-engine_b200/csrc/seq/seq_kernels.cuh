@@ -15,8 +15,9 @@ int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, in
 int launch_axpby(float* y, float a, const float* y2, float b, size_t count, cudaStream_t s);
 // y = [res +] w * x / sqrt(mean_g(x^2) + eps) per row and per group of W / groups consecutive elements.  x, y, res float [n, W] with row
 // strides ldx / ldy (res shares ldy; y may alias res); rows: optional gather of the input AND residual rows.  y_t: optional T copy of y.
+// x2 (optional, same layout as x): the input is a * x + b * x2.
 int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
-                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s);
+                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s, const float* x2 = nullptr, float a = 1.f, float b = 0.f);
 // x[i, :] = table[tokens[i], :] + sinusoidal position vector of tok_pos[i] (entry 2k sin, 2k + 1 cos of pos * base^(-2k / W)); x_t: optional T copy
 int launch_embed_pos(int dt, const void* table, const int32_t* tokens, const int32_t* tok_pos, int n, int W, float base, float* x, void* x_t, cudaStream_t s);
 // x_t T [n, W] = x float [n, W] rounded to the storage type (dense rows)

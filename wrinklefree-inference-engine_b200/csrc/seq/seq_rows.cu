@@ -133,20 +133,22 @@ int launch_add_bias(int dt, float* y, int ld, const void* bias, int n, int W, cu
     return launch_check(cudaGetLastError(), "add_bias");
 }
 
-// one block per (row, group)
+// one block per (row, group).  x2 (optional): the normalised quantity is a * x + b * x2 (two mixers' outputs combined on the way in)
 template <typename T>
 __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const T* __restrict__ w, int gw, float eps, const float* res,
-                                     float* y, int ldy, T* __restrict__ y_t, int ldt, const int32_t* __restrict__ rows) {
+                                     float* y, int ldy, T* __restrict__ y_t, int ldt, const int32_t* __restrict__ rows, const float* __restrict__ x2, float a,
+                                     float b) {
     __shared__ float scratch[33];
     const int i = blockIdx.x, g = blockIdx.y;
     const int src = rows ? rows[i] : i;
     const float* xr = x + (size_t)src * ldx + (size_t)g * gw;
+    const float* xr2 = x2 ? x2 + (size_t)src * ldx + (size_t)g * gw : nullptr;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < gw; c += blockDim.x) { const float v = xr[c]; ss += v * v; }
+    for (int c = threadIdx.x; c < gw; c += blockDim.x) { const float v = xr2 ? a * xr[c] + b * xr2[c] : xr[c]; ss += v * v; }
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)gw + eps);
     for (int c = threadIdx.x; c < gw; c += blockDim.x) {
-        float v = xr[c] * inv * to_f(w[g * gw + c]);
+        float v = (xr2 ? a * xr[c] + b * xr2[c] : xr[c]) * inv * to_f(w[g * gw + c]);
         if (res) v += res[(size_t)src * ldy + g * gw + c];
         if (y) y[(size_t)i * ldy + g * gw + c] = v;
         if (y_t) y_t[(size_t)i * ldt + g * gw + c] = from_f<T>(v);
@@ -154,15 +156,15 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const
 }
 
 int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
-                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s) {
+                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s, const float* x2, float a, float b) {
     if (n <= 0) return WF_OK;
     if (groups <= 0 || W % groups) { set_error("group_rmsnorm: width %d not divisible into %d groups", W, groups); return WF_ERR_INVALID; }
     if (res && rows && y == res) { set_error("group_rmsnorm: gathered rows cannot be added in place"); return WF_ERR_INVALID; }
     const int gw = W / groups;
     const int threads = gw >= 2048 ? 512 : (gw >= 1024 ? 256 : (gw >= 256 ? 128 : 64));
     dim3 grid(n, groups);
-    if (dt == WF_BF16) group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const __nv_bfloat16*)w, gw, eps, res, y, ldy, (__nv_bfloat16*)y_t, ldt, rows);
-    else group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const float*)w, gw, eps, res, y, ldy, (float*)y_t, ldt, rows);
+    if (dt == WF_BF16) group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const __nv_bfloat16*)w, gw, eps, res, y, ldy, (__nv_bfloat16*)y_t, ldt, rows, x2, a, b);
+    else group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const float*)w, gw, eps, res, y, ldy, (float*)y_t, ldt, rows, x2, a, b);
     return launch_check(cudaGetLastError(), "group_rmsnorm");
 }
 
