@@ -84,8 +84,8 @@ typedef struct wf_seq_layer {
      * the other's 'l<i>.mix.right.*'. */
     int pair;
     float mix_scale, pair_scale;
-    /* tied = 1: the layer has no tensors of its own and uses those of layer tied_to (an earlier layer with the same descriptor); its
-     * cache rows and its state are its own. */
+    /* tied = 1: the layer has no tensors of its own and uses those of layer tied_to (another layer, untied, with the same descriptor;
+     * it may come later); its cache rows and its state are its own. */
     int tied, tied_to;
 } wf_seq_layer;
 

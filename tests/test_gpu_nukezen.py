@@ -38,7 +38,9 @@ def config(layers, width=48, vocab=61, eps=2e-5, escale=1.7):
 
 _P0 = par(ff=40)
 # (config, sizes the tensor shapes give): layer order, head groupings, taps, ranks and table sizes all differ between them
-CFG_MIXED = (config([_P0, cdelta(), tied(_P0, 0), catt(ff=56)]), {1: {"rank_a": 5, "rank_g": 7}, 3: {"rel_rows": 10}})
+_A3 = catt(ff=56)
+# the last layer is tied BACK to an attention layer, the first one FORWARD to the paired layer at index 2
+CFG_MIXED = (config([tied(_P0, 2), cdelta(), _P0, _A3, tied(_A3, 3)]), {1: {"rank_a": 5, "rank_g": 7}, 3: {"rel_rows": 10}})
 _D1 = cdelta(heads=3, kv=3, dim=6, vdim=10, conv=2, ff=20)
 # equal head counts, one head per group and one group for all, three norm groups, every entry rotated, a window of one token, an odd table,
 # a tie between recurrent layers, nothing a multiple of 8

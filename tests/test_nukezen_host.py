@@ -62,7 +62,7 @@ def test_config_reader_rejects_what_it_cannot_serve():
     bad = dict(cs[0], layers=[dict(cs[0]["layers"][0], type="mystery")])
     with pytest.raises(ValueError):
         NukezenConfig.from_dict(bad, shapes).native_layers()
-    fwd = dict(cs[0], layers=[dict(cs[0]["layers"][0], weights_of=0)])
+    fwd = dict(cs[0], layers=[dict(cs[0]["layers"][2], weights_of=0)])
     with pytest.raises(ValueError):
         NukezenConfig.from_dict(fwd, shapes).native_layers()
     with pytest.raises(ValueError):
@@ -108,15 +108,15 @@ def test_oracle_is_sensitive_to_every_mechanism():
     w2 = dict(w); w2["l3.mix.rel"] = torch.zeros_like(w["l3.mix.rel"])
     assert float(rel_err(O.chunk_attention(h, w2, "l3.mix.", a, eps).numpy(), base.numpy()).max()) > 1e-2
     le = cfg["layers"][0]["mixer"]["left"]
-    base = O.window_attention(h, w, "l0.mix.left.", le, eps)
+    base = O.window_attention(h, w, "l2.mix.left.", le, eps)
     for change in ({"mask": {"size": 8}}, {"rot": {"dims": 6, "base": 1000.0}}, {"rot": {"dims": 8, "base": 900.0}}, {"kv_heads": 4}):
         if "kv_heads" in change:
             continue
-        assert float(rel_err(O.window_attention(h, w, "l0.mix.left.", dict(le, **change), eps).numpy(), base.numpy()).max()) > 1e-3, change
+        assert float(rel_err(O.window_attention(h, w, "l2.mix.left.", dict(le, **change), eps).numpy(), base.numpy()).max()) > 1e-3, change
     ri = cfg["layers"][0]["mixer"]["right"]
-    base = O.state_space(h, w, "l0.mix.right.", ri, eps)
+    base = O.state_space(h, w, "l2.mix.right.", ri, eps)
     for nm in ("D", "dt_bias", "A_log", "conv.b"):
-        w2 = dict(w); w2["l0.mix.right." + nm] = w["l0.mix.right." + nm] + 0.5
-        assert float(rel_err(O.state_space(h, w2, "l0.mix.right.", ri, eps).numpy(), base.numpy()).max()) > 1e-2, nm
+        w2 = dict(w); w2["l2.mix.right." + nm] = w["l2.mix.right." + nm] + 0.5
+        assert float(rel_err(O.state_space(h, w2, "l2.mix.right.", ri, eps).numpy(), base.numpy()).max()) > 1e-2, nm
 
 

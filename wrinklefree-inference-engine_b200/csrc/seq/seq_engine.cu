@@ -163,10 +163,10 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
         if (i >= c.n_layers && (l.pair || l.has_ff || l.tied)) { set_error("mixer %d: a second mixer has no pair, feed-forward or tie of its own", i); return WF_ERR_INVALID; }
         if (l.pair && (l.pair < c.n_layers || l.pair >= c.n_layers + c.n_extra)) { set_error("layer %d: pair %d is not a second-mixer entry", i, l.pair); return WF_ERR_INVALID; }
         if (l.tied) {
-            const wf_seq_layer* src = l.tied_to >= 0 && l.tied_to < i ? &L[l.tied_to] : nullptr;
+            const wf_seq_layer* src = l.tied_to >= 0 && l.tied_to < c.n_layers && l.tied_to != i ? &L[l.tied_to] : nullptr;
             if (!src || src->tied || src->type != l.type || src->heads != l.heads || src->dim != l.dim || src->vdim != l.vdim || src->kv_heads != l.kv_heads ||
                 src->has_ff != l.has_ff || src->ff != l.ff || (src->pair != 0) != (l.pair != 0) || src->conv != l.conv) {
-                set_error("layer %d: tied_to %d must name an earlier untied layer of the same shape", i, l.tied_to); return WF_ERR_INVALID;
+                set_error("layer %d: tied_to %d must name another layer, with weights of its own and the same shape", i, l.tied_to); return WF_ERR_INVALID;
             }
             if (l.pair && (L[l.pair].type != L[src->pair].type || L[l.pair].heads != L[src->pair].heads || L[l.pair].dim != L[src->pair].dim ||
                            L[l.pair].vdim != L[src->pair].vdim || L[l.pair].kv_heads != L[src->pair].kv_heads || L[l.pair].conv != L[src->pair].conv)) {
@@ -434,7 +434,7 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
         }
         if ((rc = launch_gqa_attn_mma(b, D, e->qn, gate, pc, e->og, e->gqa_ws, splits, s))) return rc;
     } else if ((rc = launch_gqa_attn(e->dt, b, D, e->qn, gate, pc, e->og, s))) return rc;
-    mark(e, "attn.attention");
+    mark(e, D.softcap > 0.f || D.rel ? "attn.attention(cap+bias)" : "attn.attention");
     rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, out, 1, W, n, W, nv), s);
     // the single-gain norm of the post form takes the bias itself, except for paired mixers (their outputs are combined first)
     if (!rc && L.ob && !(e->cfg.block_form == WF_SEQ_BLOCK_POST && !e->cfg.norm_weights && !L.c.pair && out == e->y)) rc = launch_add_bias(e->dt, out, W, L.ob, n, W, s);
@@ -848,7 +848,12 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
         return WF_OK;
     };
     const size_t lnorm = post ? norm_elems : (size_t)W;
-    for (int li = 0; li < c.n_layers; ++li) {
+    // layers with weights of their own first, then the tied ones (a tie may point forward); the order only decides where a layer's part
+    // of a page and of a state slot lies
+    std::vector<int> order;
+    for (int li = 0; li < c.n_layers; ++li) if (!layers[li].tied) order.push_back(li);
+    for (int li = 0; li < c.n_layers; ++li) if (layers[li].tied) order.push_back(li);
+    for (int li : order) {
         LayerState& L = e->layers[li];
         own = !layers[li].tied;
         if (!own) L = e->layers[layers[li].tied_to];      // the source's weight pointers; offsets of cache and state are assigned anew below

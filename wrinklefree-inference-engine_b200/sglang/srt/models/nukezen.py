@@ -108,8 +108,8 @@ class NukezenConfig:
         n = len(self.layers)
         for i, L in enumerate(self.layers):
             src = L.get("weights_of")
-            if src is not None and not (0 <= int(src) < i and self.layers[int(src)].get("weights_of") is None):
-                raise ValueError(f"config: layer {i} takes its weights from layer {src}, which is not an earlier layer with weights of its own")
+            if src is not None and not (0 <= int(src) < n and int(src) != i and self.layers[int(src)].get("weights_of") is None):
+                raise ValueError(f"config: layer {i} takes its weights from layer {src}, which is not another layer with weights of its own")
             prefix = f"l{i if src is None else int(src)}."
             m, kind = L["mixer"], L["type"]
             if kind == "parallel":
