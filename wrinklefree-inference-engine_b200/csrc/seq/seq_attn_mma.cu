@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
         r_slope2[k] = D.dist_exp > 0.f ? exp2f(-D.dist_exp * (float)(r_head[k] + 1) / (float)D.H) * LOG2E : 0.f;
     }
     const float scale2 = D.scale * LOG2E;
+    const float cap2 = D.softcap > 0.f ? 2.f / D.softcap : 0.f;
     // first and last position among the rows of this warp that exist
     const int wpos_min = pos0 + (row_base >> ap.rp2_log);
     const int wpos_max = pos0 + ((row_base + 15) >> ap.rp2_log) < pos_last ? pos0 + ((row_base + 15) >> ap.rp2_log) : pos_last;
@@ -227,8 +228,10 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
                     const int dist = r_pos[k] - key;
                     const bool vis = whole || (r_ok[k] && dist >= 0 && key >= r_lo[k]);
                     float v = s[j][e] * D.scale;
-                    if (D.softcap > 0.f) v = D.softcap * tanhf(v / D.softcap);
-                    if (D.rel) { const int dd = dist < 0 ? 0 : (dist < D.rel_n ? dist : D.rel_n - 1); v += __ldg(D.rel + (size_t)dd * D.H + r_head[k]); }
+                    // cap * tanh(v / cap) as cap * (1 - 2 / (exp(2 v / cap) + 1)): the hardware exponential and reciprocal keep the
+                    // score to a few 1e-6 of the cap, well inside what the bf16 operands of the product leave
+                    if (D.softcap > 0.f) v = D.softcap * (1.f - __fdividef(2.f, __expf(v * cap2) + 1.f));
+                    if (D.rel) { const int dd = max(0, min(dist, D.rel_n - 1)); v += __ldg(D.rel + dd * D.H + r_head[k]); }
                     v = vis ? fmaf(v, LOG2E, -r_slope2[k] * (float)dist) : -INFINITY;
                     s[j][e] = v;
                     mx[k] = fmaxf(mx[k], v);
