@@ -364,6 +364,24 @@ def test_state_is_carried_over_hundreds_of_tokens():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_of_the_state_space_recurrence(dtype):
+    """Portions of several hundred tokens run the state-space recurrence in parallel chunks (every chunk from a zero state, the start
+    states chained, every chunk again): a long portion after a short one, then a ragged batch of a long, a short and a chunk-sized
+    portion in three slots, against the token-by-token oracle."""
+    cfg = config([par(ls=0.0, rs=1.0, sh=3, sp=10, sn=12, sg=3, conv=4, ng=1)], width=32)
+    w = make_weights((cfg, {}), 161)
+    m = build(cfg, w, dtype, max_tokens=4096, page_size=16, max_step_tokens=1024)
+    rows = [_rows(n, 32, 162 + n) for n in (37 + 600, 5 + 128, 300 + 1)]
+    want = [oracle_mixer(cfg, w, 0, r) for r in rows]
+    assert_close(part_alone(m, 0, 2, rows[0], [37, 600]), want[0], dtype, "one slot", 2.0)
+    slots = [m.admit() for _ in rows]
+    got = m.engine.run_part(0, 2, slots, [37, 5, 300], np.concatenate([rows[0][:37], rows[1][:5], rows[2][:300]]))
+    got2 = m.engine.run_part(0, 2, slots, [600, 128, 1], np.concatenate([rows[0][37:], rows[1][5:], rows[2][300:]]))
+    assert_close(np.concatenate([got, got2]), np.concatenate([want[0][:37], want[1][:5], want[2][:300], want[0][37:], want[1][5:], want[2][300:]]), dtype, "ragged", 2.0)
+    m.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_over_page_borders(dtype):
     """150 decoded tokens on 4-token pages: windows, chunks and bias buckets slide over decoded tokens only."""
     cs = CONFIGS["mixed"]

@@ -24,6 +24,7 @@ struct Batch {
     const int32_t* seq_len;    // [nseq] tokens of the sequence in this step
     const int32_t* seq_pos0;   // [nseq] position of its first token
     const int32_t* seq_slot;   // [nseq] state slot = block-table row
+    int max_len = 0;           // longest portion of the step (known on the host; sizes grids that cut portions into chunks)
 };
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -71,6 +71,12 @@ __global__ void ssd_post_kernel(int H, int dv, int groups, const float* __restri
 
 constexpr int DR_THREADS = 128, DR_TT = 16;
 
+// chunked run of a linear recurrence: pass 0 = whole portions in order (no chunks); pass 1 = a block takes one chunk from a ZERO state and
+// leaves its end state (and the product of its decays) in the workspace; pass 3 = a block takes one chunk from the start state that
+// scan_prefix_kernel chained and writes the outputs.  Workspace entry of (sequence, chunk): seq_start / chunk + sequence + chunk, which
+// never collides between sequences and stays below tokens / chunk + sequences.
+struct ScanArgs { int pass = 0, chunk = 0, nchunks = 1; float* local = nullptr; float* start = nullptr; float* prod = nullptr; };
+
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
@@ -85,21 +91,37 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
 template <int DPT, int DR_PARTS, bool VEC, bool DELTA>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDims D, const float* __restrict__ qkv, int ld,
                                                                          const float* __restrict__ beta, const float* __restrict__ decay,
-                                                                         float* __restrict__ state, size_t slot_stride, float* __restrict__ o) {
+                                                                         float* __restrict__ state, size_t slot_stride, float* __restrict__ o, ScanArgs sa) {
     constexpr int DR_COLS = DR_THREADS / DR_PARTS;
     extern __shared__ float sm[];
     const int tile_floats = (VEC ? 3 : 2) * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][d], q [TT][d], v [TT][cols], beta [TT], decay [TT], vector decay [TT][d]
-    const int sq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
+    const int sq = sa.pass ? blockIdx.x / sa.nchunks : blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
     const int tid = threadIdx.x, p = tid % DR_PARTS, jl = tid / DR_PARTS, col = col0 + jl;
     const bool col_ok = col < D.dv;
     const int kh = h / (D.H / D.Hk);
-    const int start = b.seq_start[sq], len = b.seq_len[sq];
-    float* S = state + (size_t)b.seq_slot[sq] * slot_stride + (size_t)h * D.d * D.dv;
+    int start = b.seq_start[sq], len = b.seq_len[sq];
+    float* S = state + (size_t)b.seq_slot[sq] * slot_stride + (size_t)h * D.d * D.dv;      // where the state is read ...
+    float* S_out = S;                                                                        // ... and where it is left
+    if (sa.pass) {
+        const int c = blockIdx.x - sq * sa.nchunks;
+        if (c * sa.chunk >= len) return;                                                     // the whole block: this sequence has fewer chunks
+        const size_t entry = ((size_t)(start / sa.chunk + sq + c) * D.H + h) * D.d * D.dv;
+        S = sa.pass == 1 ? nullptr : sa.start + entry;
+        S_out = sa.pass == 1 ? sa.local + entry : nullptr;
+        if (sa.pass == 1 && tid == 0 && blockIdx.z == 0) {                                   // the chunk's decay product (one decay per head)
+            float pr = 1.f;
+            const int t1 = len - c * sa.chunk < sa.chunk ? len - c * sa.chunk : sa.chunk;
+            for (int t = 0; t < t1; ++t) pr *= decay[(size_t)(start + c * sa.chunk + t) * D.H + h];
+            sa.prod[(size_t)(start / sa.chunk + sq + c) * D.H + h] = pr;
+        }
+        start += c * sa.chunk;
+        len = len - c * sa.chunk < sa.chunk ? len - c * sa.chunk : sa.chunk;
+    }
     float s[DPT];
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
         const int i = p + DR_PARTS * m;
-        s[m] = (col_ok && i < D.d) ? S[(size_t)i * D.dv + col] : 0.f;
+        s[m] = (S && col_ok && i < D.d) ? S[(size_t)i * D.dv + col] : 0.f;
     }
     const int q_off = (D.q_off >= 0 ? D.q_off : 0) + kh * D.d, k_off = (D.k_off >= 0 ? D.k_off : D.Hk * D.d) + kh * D.d,
               v_off = (D.v_off >= 0 ? D.v_off : 2 * D.Hk * D.d) + h * D.dv;
@@ -181,14 +203,31 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
             os += __shfl_xor_sync(0xffffffffu, os, 1);
             os += __shfl_xor_sync(0xffffffffu, os, 2);
             if (DR_PARTS == 8) os += __shfl_xor_sync(0xffffffffu, os, 4);
-            if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = os;
+            if (p == 0 && col_ok && sa.pass != 1) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = os;
         }
     }
+    if (!S_out) return;
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
         const int i = p + DR_PARTS * m;
-        if (col_ok && i < D.d) S[(size_t)i * D.dv + col] = s[m];
+        if (col_ok && i < D.d) S_out[(size_t)i * D.dv + col] = s[m];
     }
+}
+
+// thread per (sequence, head, state element): chains the chunks' start states from the slot's state and leaves the end state in the slot
+__global__ void scan_prefix_kernel(Batch b, int H, int dd, int chunk, float* __restrict__ state, size_t slot_stride, const float* __restrict__ local,
+                                   float* __restrict__ startws, const float* __restrict__ prod) {
+    const int sq = blockIdx.x, h = blockIdx.y, e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= dd) return;
+    const int len = b.seq_len[sq], nc = (len + chunk - 1) / chunk, base = b.seq_start[sq] / chunk + sq;
+    float* Sp = state + (size_t)b.seq_slot[sq] * slot_stride + (size_t)h * dd + e;
+    float S = *Sp;
+    for (int c = 0; c < nc; ++c) {
+        const size_t entry = (size_t)(base + c) * H + h;
+        startws[entry * dd + e] = S;
+        S = fmaf(prod[entry], S, local[entry * dd + e]);
+    }
+    *Sp = S;
 }
 
 template <typename T>
@@ -223,10 +262,10 @@ int launch_delta_prep(int dt, const DeltaDims& D, int n, float* qkv, int ld, con
 namespace {
 template <bool VEC, bool DELTA>
 int delta_rule_launch(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
-                      size_t slot_stride, float* o, cudaStream_t s) {
+                      size_t slot_stride, float* o, cudaStream_t s, ScanArgs sa = ScanArgs()) {
     const bool decode = b.n == b.nseq;                     // every sequence brings one token
     const int parts = decode ? 4 : 8, cols = DR_THREADS / parts;
-    dim3 grid(b.nseq, D.H, (D.dv + cols - 1) / cols);
+    dim3 grid(sa.pass ? b.nseq * sa.nchunks : b.nseq, D.H, (D.dv + cols - 1) / cols);
     const size_t smem = 2 * ((size_t)(VEC ? 3 : 2) * DR_TT * D.d + DR_TT * cols + 2 * DR_TT) * sizeof(float);   // two token groups
     static DevOnce once;
     if (once.need()) {
@@ -235,7 +274,7 @@ int delta_rule_launch(const Batch& b, const DeltaDims& D, const float* qkv, int 
 #undef DR_ATTR
     }
     const int dpt = (D.d + parts - 1) / parts;
-#define DR_LAUNCH(dp, pa) delta_rule_kernel<dp, pa, VEC, DELTA><<<grid, DR_THREADS, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o)
+#define DR_LAUNCH(dp, pa) delta_rule_kernel<dp, pa, VEC, DELTA><<<grid, DR_THREADS, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o, sa)
     if (D.d > 256 || smem > 160 * 1024) { set_error("delta: key dimension %d above the supported 256", D.d); return WF_ERR_UNSUPPORTED; }
     if (decode) { if (dpt <= 8) DR_LAUNCH(8, 4); else if (dpt <= 16) DR_LAUNCH(16, 4); else if (dpt <= 32) DR_LAUNCH(32, 4); else DR_LAUNCH(64, 4); }
     else { if (dpt <= 8) DR_LAUNCH(8, 8); else if (dpt <= 16) DR_LAUNCH(16, 8); else if (dpt <= 32) DR_LAUNCH(32, 8); else DR_LAUNCH(64, 8); }
@@ -245,11 +284,24 @@ int delta_rule_launch(const Batch& b, const DeltaDims& D, const float* qkv, int 
 }  // namespace
 
 int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
-                      size_t slot_stride, float* o, cudaStream_t s) {
+                      size_t slot_stride, float* o, cudaStream_t s, const ScanWorkspace* scan) {
     if (b.nseq <= 0) return WF_OK;
     if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
     if (D.no_delta) {
         if (D.vec_decay) { set_error("delta: the plain recurrence takes one decay per head"); return WF_ERR_UNSUPPORTED; }
+        // long portions: chunks in parallel (two short sequential passes instead of one long one)
+        if (scan && scan->local && b.n != b.nseq && b.max_len >= 2 * SCAN_CHUNK && b.n / SCAN_CHUNK + b.nseq + 1 <= scan->chunks) {
+            ScanArgs sa;
+            sa.chunk = SCAN_CHUNK; sa.nchunks = (b.max_len + SCAN_CHUNK - 1) / SCAN_CHUNK;
+            sa.local = scan->local; sa.start = scan->start; sa.prod = scan->prod;
+            sa.pass = 1;
+            if (int rc = delta_rule_launch<false, false>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s, sa)) return rc;
+            const int dd = D.d * D.dv;
+            scan_prefix_kernel<<<dim3(b.nseq, D.H, (dd + 255) / 256), 256, 0, s>>>(b, D.H, dd, SCAN_CHUNK, state, slot_stride, scan->local, scan->start, scan->prod);
+            if (int rc = launch_check(cudaGetLastError(), "scan_prefix")) return rc;
+            sa.pass = 3;
+            return delta_rule_launch<false, false>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s, sa);
+        }
         return delta_rule_launch<false, false>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s);
     }
     return D.vec_decay ? delta_rule_launch<true, true>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s)

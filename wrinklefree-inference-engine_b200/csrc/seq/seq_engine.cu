@@ -92,6 +92,7 @@ struct wf_seq_engine {
     float *gate = nullptr, *ugu = nullptr, *uy = nullptr;      // head gates; the every-token unit's [gate | up] rows and its output
     float *y2 = nullptr;              // output of the second mixer of a paired layer
     float *gfull = nullptr, *afull = nullptr;   // recurrences: gate and decay logits when they are products of two matrices
+    ScanWorkspace scan;               // state-space recurrence over long portions: per-chunk states (launch_delta_rule)
     void* uhmid = nullptr;
     int32_t *ids = nullptr, *counts = nullptr, *plan_scratch = nullptr, *sorted_rows = nullptr, *pair_row = nullptr, *tile_group = nullptr;
     int P = 0;                        // padded expert-row bound
@@ -267,6 +268,8 @@ int prepare_step(wf_seq_engine* e, int nseq, const int32_t* slots, const int32_t
     int32_t* d = e->d_meta;
     v->tokens = d;
     v->b.n = n; v->b.nseq = nseq;
+    v->b.max_len = 0;
+    for (int i = 0; i < nseq; ++i) v->b.max_len = std::max(v->b.max_len, (int)counts[i]);
     v->b.tok_seq = d + T; v->b.tok_pos = d + 2 * T;
     v->b.seq_start = d + 3 * T; v->b.seq_len = d + 3 * T + S; v->b.seq_pos0 = d + 3 * T + 2 * S; v->b.seq_slot = d + 3 * T + 3 * S;
     v->want = d + 3 * T + 4 * S;
@@ -390,7 +393,7 @@ int run_ssd(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     mark(e, "ssd.conv+prep");
     DeltaDims D{H, c.kv_heads, c.dim, c.vdim};
     D.no_delta = 1; D.v_off = 0; D.k_off = inner; D.q_off = inner + GN;
-    if ((rc = launch_delta_rule(b, D, e->qkvc, C, e->beta, e->decay, e->state + L.st_S, e->slot_stride, e->od, s))) return rc;
+    if ((rc = launch_delta_rule(b, D, e->qkvc, C, e->beta, e->decay, e->state + L.st_S, e->slot_stride, e->od, s, &e->scan))) return rc;
     mark(e, "ssd.recurrence");
     if ((rc = launch_ssd_post(e->dt, n, H, c.vdim, c.out_norm_groups, e->od, e->qkvc, C, e->proj, L.np, L.Dskip, L.onorm, e->cfg.eps, e->og, s))) return rc;
     mark(e, "ssd.post");
@@ -730,7 +733,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     long long cache_elems = 0;
     size_t st = 0;
     e->layers.resize(c.n_layers + c.n_extra);
-    size_t max_gate = 1, max_decay = 1, max_gfull = 0, max_afull = 0;
+    size_t max_gate = 1, max_decay = 1, max_gfull = 0, max_afull = 0, max_scan = 0;
     bool own = true;                 // false while a tied layer is laid out: it allocates and names nothing, its weights are its source's
     auto walloc = [&](void** ptr, size_t count) -> int { return own ? dalloc_t(e, ptr, count) : WF_OK; };
     auto name = [&](const std::string& n, void* dst, size_t count) { if (own) add_tensor(e, n, dst, count); };
@@ -813,6 +816,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
             L.st_conv = st; st += (size_t)(l.conv - 1) * L.C;
             L.st_S = st; st += (size_t)l.heads * l.dim * l.vdim;
             max_C = std::max(max_C, (size_t)L.C);
+            max_scan = std::max(max_scan, (size_t)l.heads * l.dim * l.vdim);
         } else {
             // [q | k | v | gate (or its first factor) | write strength | decay (or its first factor)]
             const size_t nqk = (size_t)l.kv_heads * l.dim;
@@ -944,6 +948,11 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     if (e->dt == WF_BF16 && max_hr > 1) TRY(dalloc_bytes(e, (void**)&e->attn_ws, (size_t)e->attn_ws_rows * (max_hr + 2 * max_H) * sizeof(float)));
     TRY(dalloc_n(e, &e->gate, (size_t)T * std::max(max_H, max_gate)));
     if (c.n_extra > 0) TRY(dalloc_n(e, &e->y2, (size_t)T * W));
+    if (max_scan && T >= 2 * SCAN_CHUNK) {
+        e->scan.chunks = scan_chunks_needed(T, c.slots);
+        TRY(dalloc_n(e, &e->scan.local, (size_t)e->scan.chunks * max_scan)); TRY(dalloc_n(e, &e->scan.start, (size_t)e->scan.chunks * max_scan));
+        TRY(dalloc_n(e, &e->scan.prod, (size_t)e->scan.chunks * max_H));
+    }
     if (max_gfull) TRY(dalloc_n(e, &e->gfull, (size_t)T * max_gfull));
     if (max_afull) TRY(dalloc_n(e, &e->afull, (size_t)T * max_afull));
     if (e->dt == WF_BF16 && max_gqa_dv) { e->gqa_ws_rows = 32768; TRY(dalloc_bytes(e, (void**)&e->gqa_ws, gqa_attn_mma_workspace(e->gqa_ws_rows, 1, (int)max_gqa_dv))); }

@@ -152,8 +152,14 @@ struct DeltaDims { int H, Hk, d, dv; int vec_decay = 0, no_delta = 0, q_off = -1
 int launch_delta_prep(int dt, const DeltaDims& D, int n, float* qkv, int ld, const float* a_raw, int lda, const float* b_raw, int ldb_,
                       const void* A_log, const void* dt_bias, float* beta, float* decay, cudaStream_t s);
 // per (sequence, head): for each token in order  S = decay S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q.   S float [slot][H][d][dv]
+// scan (optional, no_delta form with one decay per head only): long portions are cut into chunks of SCAN_CHUNK tokens that run in parallel —
+// every chunk's own contribution from a zero state, a short pass that chains the chunks' start states (S_start[c + 1] = prod_c S_start[c]
+// + local_c, the recurrence being linear in the state), then every chunk again from its start state for the outputs.
+constexpr int SCAN_CHUNK = 128;
+struct ScanWorkspace { float* local = nullptr; float* start = nullptr; float* prod = nullptr; int chunks = 0; };   // chunks: entries of H * d * dv floats each
+inline int scan_chunks_needed(int max_step_tokens, int slots) { return max_step_tokens / SCAN_CHUNK + slots + 1; }
 int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int ld, const float* beta, const float* decay, float* state,
-                      size_t slot_stride, float* o, cudaStream_t s);
+                      size_t slot_stride, float* o, cudaStream_t s, const ScanWorkspace* scan = nullptr);
 // y T [n, H * dv] = o / sqrt(mean_dv(o^2) + eps) * w[dv] * act(g float [n, H * dv] (ldg)); act 0 silu, 1 sigmoid
 int launch_delta_post(int dt, const DeltaDims& D, int n, const float* o, const void* w, float eps, const float* g, int ldg, void* y, cudaStream_t s, int act = 0);
 // state-space recurrence around launch_delta_rule (no_delta form).  prep: step[n, H] = softplus(dt_raw + dt_bias[h]) (no clamp),
