@@ -81,9 +81,9 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
 
-// block = (sequence, head, 16 value columns); thread = (column, eighth of the key rows), its part of the column in registers.
+// block = (sequence, head, 16 value columns); thread = (column, eighth of the key rows: DPT consecutive ones), its part of the column in registers.
 // Tokens are taken 16 at a time: the next group's k / q / v / gates are copied into the other half of shared memory (cp.async)
-// while the current group runs, so the per-token chain is only register math, shared-memory broadcasts and two quad reductions.
+// while the current group runs, so the per-token chain is only register math, 16-byte shared-memory reads and two quad reductions.
 // DR_PARTS = 8 (16 columns per block): short per-token chains and twice the blocks, for portions of many tokens;
 // DR_PARTS = 4 (32 columns): wider, better coalesced state rows, for single decoded tokens where the state traffic is the cost.
 // VEC: the decay is a vector over the key rows (staged per token like k and q) instead of one number per token.
@@ -93,8 +93,11 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
                                                                          const float* __restrict__ beta, const float* __restrict__ decay,
                                                                          float* __restrict__ state, size_t slot_stride, float* __restrict__ o, ScanArgs sa) {
     constexpr int DR_COLS = DR_THREADS / DR_PARTS;
-    extern __shared__ float sm[];
-    const int tile_floats = (VEC ? 3 : 2) * DR_TT * D.d + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][d], q [TT][d], v [TT][cols], beta [TT], decay [TT], vector decay [TT][d]
+    extern __shared__ __align__(16) float sm[];
+    // A thread owns DPT consecutive key rows; a token's k / q / decay rows lie in shared memory with 4 floats of padding after every DPT, so
+    // that the eight (or four) threads of a column read their parts as 16-byte vectors from distinct banks.
+    constexpr int PS = DPT + 4, RS = DR_PARTS * PS;           // floats per part and per token row
+    constexpr int tile_floats = (VEC ? 3 : 2) * DR_TT * RS + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][RS], q [TT][RS], v [TT][cols], beta [TT], decay [TT], vector decay [TT][RS]
     const int sq = sa.pass ? blockIdx.x / sa.nchunks : blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
     const int tid = threadIdx.x, p = tid % DR_PARTS, jl = tid / DR_PARTS, col = col0 + jl;
     const bool col_ok = col < D.dv;
@@ -120,25 +123,26 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
     float s[DPT];
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
-        const int i = p + DR_PARTS * m;
+        const int i = p * DPT + m;
         s[m] = (S && col_ok && i < D.d) ? S[(size_t)i * D.dv + col] : 0.f;
     }
     const int q_off = (D.q_off >= 0 ? D.q_off : 0) + kh * D.d, k_off = (D.k_off >= 0 ? D.k_off : D.Hk * D.d) + kh * D.d,
               v_off = (D.v_off >= 0 ? D.v_off : 2 * D.Hk * D.d) + h * D.dv;
     auto stage = [&](int buf, int t0) {
         float* ks = sm + (size_t)buf * tile_floats;
-        float* qs = ks + DR_TT * D.d;
-        float* vs = qs + DR_TT * D.d;
+        float* qs = ks + DR_TT * RS;
+        float* vs = qs + DR_TT * RS;
         float* bs = vs + DR_TT * DR_COLS;
         float* gs = bs + DR_TT;
         float* gv = gs + DR_TT;
         const int tt = len - t0 < DR_TT ? len - t0 : DR_TT;
         for (int idx = tid; idx < tt * D.d; idx += blockDim.x) {
             const int t = idx / D.d, c = idx - t * D.d;
+            const int at = t * RS + c + (c / DPT) * 4;        // the padded place of row c
             const float* row = qkv + (size_t)(start + t0 + t) * ld;
-            cp_async4(ks + idx, row + k_off + c);
-            cp_async4(qs + idx, row + q_off + c);
-            if (VEC) cp_async4(gv + idx, decay + ((size_t)(start + t0 + t) * D.H + h) * D.d + c);
+            cp_async4(ks + at, row + k_off + c);
+            cp_async4(qs + at, row + q_off + c);
+            if (VEC) cp_async4(gv + at, decay + ((size_t)(start + t0 + t) * D.H + h) * D.d + c);
         }
         for (int idx = tid; idx < tt * DR_COLS; idx += blockDim.x) {
             const int t = idx / DR_COLS, c = idx % DR_COLS;
@@ -159,30 +163,40 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
         __syncthreads();                                      // group t0 landed; everyone is done with the other half
         if (t0 + DR_TT < len) stage(buf ^ 1, t0 + DR_TT);
         const float* ks = sm + (size_t)buf * tile_floats;
-        const float* qs = ks + DR_TT * D.d;
-        const float* vs = qs + DR_TT * D.d;
+        const float* qs = ks + DR_TT * RS;
+        const float* vs = qs + DR_TT * RS;
         const float* bs = vs + DR_TT * DR_COLS;
         const float* gs = bs + DR_TT;
         const float* gv = gs + DR_TT;
+        const int i0 = p * DPT;                               // this thread's first key row
         for (int t = 0; t < tt; ++t) {
-            const float* kt = ks + t * D.d;
-            const float* qt = qs + t * D.d;
-            const float* gt = gv + t * D.d;
+            const float4* kt = reinterpret_cast<const float4*>(ks + t * RS + p * PS);
+            const float4* qt = reinterpret_cast<const float4*>(qs + t * RS + p * PS);
+            const float4* gt = reinterpret_cast<const float4*>(gv + t * RS + p * PS);
             const float g = VEC ? 1.f : gs[t];
+            // rows at and beyond D.d hold a zero state and stay zero: what the padding or an unstaged row holds never reaches them
             if (VEC) {                                        // the rows decay first, each by its own factor
 #pragma unroll
-                for (int m = 0; m < DPT; ++m) {
-                    const int i = p + DR_PARTS * m;
-                    if (i < D.d) s[m] *= gt[i];
+                for (int m4 = 0; m4 < DPT / 4; ++m4) {
+                    const float4 gg = gt[m4];
+                    const int i = i0 + 4 * m4;
+                    if (i < D.d) s[4 * m4] *= gg.x;
+                    if (i + 1 < D.d) s[4 * m4 + 1] *= gg.y;
+                    if (i + 2 < D.d) s[4 * m4 + 2] *= gg.z;
+                    if (i + 3 < D.d) s[4 * m4 + 3] *= gg.w;
                 }
             }
             float rs = 0.f;
             if (DELTA) {
                 float r[4] = {0.f, 0.f, 0.f, 0.f};            // four chains: the sum over this thread's rows is not one dependent sequence
 #pragma unroll
-                for (int m = 0; m < DPT; ++m) {
-                    const int i = p + DR_PARTS * m;
-                    if (i < D.d) r[m & 3] = fmaf(s[m], kt[i], r[m & 3]);
+                for (int m4 = 0; m4 < DPT / 4; ++m4) {
+                    const float4 kk = kt[m4];
+                    const int i = i0 + 4 * m4;
+                    if (i < D.d) r[0] = fmaf(s[4 * m4], kk.x, r[0]);
+                    if (i + 1 < D.d) r[1] = fmaf(s[4 * m4 + 1], kk.y, r[1]);
+                    if (i + 2 < D.d) r[2] = fmaf(s[4 * m4 + 2], kk.z, r[2]);
+                    if (i + 3 < D.d) r[3] = fmaf(s[4 * m4 + 3], kk.w, r[3]);
                 }
                 rs = (r[0] + r[1]) + (r[2] + r[3]);
                 rs += __shfl_xor_sync(0xffffffffu, rs, 1);
@@ -190,26 +204,39 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
                 if (DR_PARTS == 8) rs += __shfl_xor_sync(0xffffffffu, rs, 4);
             }
             const float u = bs[t] * (vs[t * DR_COLS + jl] - g * rs);
+            if (sa.pass == 1) {                               // only the end state is wanted: no read-out
+#pragma unroll
+                for (int m4 = 0; m4 < DPT / 4; ++m4) {
+                    const float4 kk = kt[m4];
+                    const int i = i0 + 4 * m4;
+                    if (i < D.d) s[4 * m4] = fmaf(kk.x, u, g * s[4 * m4]);
+                    if (i + 1 < D.d) s[4 * m4 + 1] = fmaf(kk.y, u, g * s[4 * m4 + 1]);
+                    if (i + 2 < D.d) s[4 * m4 + 2] = fmaf(kk.z, u, g * s[4 * m4 + 2]);
+                    if (i + 3 < D.d) s[4 * m4 + 3] = fmaf(kk.w, u, g * s[4 * m4 + 3]);
+                }
+                continue;
+            }
             float out[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int m = 0; m < DPT; ++m) {
-                const int i = p + DR_PARTS * m;
-                if (i < D.d) {
-                    s[m] = fmaf(kt[i], u, g * s[m]);
-                    out[m & 3] = fmaf(s[m], qt[i], out[m & 3]);
-                }
+            for (int m4 = 0; m4 < DPT / 4; ++m4) {
+                const float4 kk = kt[m4], qq = qt[m4];
+                const int i = i0 + 4 * m4;
+                if (i < D.d) { s[4 * m4] = fmaf(kk.x, u, g * s[4 * m4]); out[0] = fmaf(s[4 * m4], qq.x, out[0]); }
+                if (i + 1 < D.d) { s[4 * m4 + 1] = fmaf(kk.y, u, g * s[4 * m4 + 1]); out[1] = fmaf(s[4 * m4 + 1], qq.y, out[1]); }
+                if (i + 2 < D.d) { s[4 * m4 + 2] = fmaf(kk.z, u, g * s[4 * m4 + 2]); out[2] = fmaf(s[4 * m4 + 2], qq.z, out[2]); }
+                if (i + 3 < D.d) { s[4 * m4 + 3] = fmaf(kk.w, u, g * s[4 * m4 + 3]); out[3] = fmaf(s[4 * m4 + 3], qq.w, out[3]); }
             }
             float os = (out[0] + out[1]) + (out[2] + out[3]);
             os += __shfl_xor_sync(0xffffffffu, os, 1);
             os += __shfl_xor_sync(0xffffffffu, os, 2);
             if (DR_PARTS == 8) os += __shfl_xor_sync(0xffffffffu, os, 4);
-            if (p == 0 && col_ok && sa.pass != 1) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = os;
+            if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = os;
         }
     }
     if (!S_out) return;
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
-        const int i = p + DR_PARTS * m;
+        const int i = p * DPT + m;
         if (col_ok && i < D.d) S_out[(size_t)i * D.dv + col] = s[m];
     }
 }
@@ -266,7 +293,8 @@ int delta_rule_launch(const Batch& b, const DeltaDims& D, const float* qkv, int 
     const bool decode = b.n == b.nseq;                     // every sequence brings one token
     const int parts = decode ? 4 : 8, cols = DR_THREADS / parts;
     dim3 grid(sa.pass ? b.nseq * sa.nchunks : b.nseq, D.H, (D.dv + cols - 1) / cols);
-    const size_t smem = 2 * ((size_t)(VEC ? 3 : 2) * DR_TT * D.d + DR_TT * cols + 2 * DR_TT) * sizeof(float);   // two token groups
+    const int dpt_raw = (D.d + parts - 1) / parts, dpt_t = dpt_raw <= 8 ? 8 : (dpt_raw <= 16 ? 16 : (dpt_raw <= 32 ? 32 : 64));
+    const size_t smem = 2 * ((size_t)(VEC ? 3 : 2) * DR_TT * parts * (dpt_t + 4) + DR_TT * cols + 2 * DR_TT) * sizeof(float);   // two token groups, padded rows
     static DevOnce once;
     if (once.need()) {
 #define DR_ATTR(dp, pa) cudaFuncSetAttribute(delta_rule_kernel<dp, pa, VEC, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
