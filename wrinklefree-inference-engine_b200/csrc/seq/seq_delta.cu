@@ -71,11 +71,16 @@ __global__ void ssd_post_kernel(int H, int dv, int groups, const float* __restri
 
 constexpr int DR_THREADS = 128, DR_TT = 16;
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
 // chunked run of a linear recurrence: pass 0 = whole portions in order (no chunks); pass 1 = a block takes one chunk from a ZERO state and
 // leaves its end state (and the product of its decays) in the workspace; pass 3 = a block takes one chunk from the start state that
 // scan_prefix_kernel chained and writes the outputs.  Workspace entry of (sequence, chunk): seq_start / chunk + sequence + chunk, which
 // never collides between sequences and stays below tokens / chunk + sequences.
-struct ScanArgs { int pass = 0, chunk = 0, nchunks = 1; float* local = nullptr; float* start = nullptr; float* prod = nullptr; };
+struct ScanArgs { int pass = 0, chunk = 0, nchunks = 1; float* local = nullptr; float* start = nullptr; float* prod = nullptr;
+                  int v4 = 0; };   // v4: every staged row starts 16-byte aligned and has a multiple of 4 entries (16-byte copies)
 
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -136,18 +141,35 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
         float* gs = bs + DR_TT;
         float* gv = gs + DR_TT;
         const int tt = len - t0 < DR_TT ? len - t0 : DR_TT;
-        for (int idx = tid; idx < tt * D.d; idx += blockDim.x) {
-            const int t = idx / D.d, c = idx - t * D.d;
-            const int at = t * RS + c + (c / DPT) * 4;        // the padded place of row c
-            const float* row = qkv + (size_t)(start + t0 + t) * ld;
-            cp_async4(ks + at, row + k_off + c);
-            cp_async4(qs + at, row + q_off + c);
-            if (VEC) cp_async4(gv + at, decay + ((size_t)(start + t0 + t) * D.H + h) * D.d + c);
-        }
-        for (int idx = tid; idx < tt * DR_COLS; idx += blockDim.x) {
-            const int t = idx / DR_COLS, c = idx % DR_COLS;
-            if (col0 + c < D.dv) cp_async4(vs + idx, qkv + (size_t)(start + t0 + t) * ld + v_off + col0 + c);
-            else vs[idx] = 0.f;
+        if (sa.v4) {
+            const int d4 = D.d >> 2;
+            for (int idx = tid; idx < tt * d4; idx += blockDim.x) {
+                const int t = idx / d4, c = (idx - t * d4) << 2;
+                const int at = t * RS + c + (c / DPT) * 4;    // the padded place of rows c .. c + 3 (DPT is a multiple of 4: one part holds them)
+                const float* row = qkv + (size_t)(start + t0 + t) * ld;
+                cp_async16(ks + at, row + k_off + c);
+                cp_async16(qs + at, row + q_off + c);
+                if (VEC) cp_async16(gv + at, decay + ((size_t)(start + t0 + t) * D.H + h) * D.d + c);
+            }
+            for (int idx = tid; idx < tt * (DR_COLS / 4); idx += blockDim.x) {
+                const int t = idx / (DR_COLS / 4), c = (idx % (DR_COLS / 4)) << 2;
+                if (col0 + c < D.dv) cp_async16(vs + t * DR_COLS + c, qkv + (size_t)(start + t0 + t) * ld + v_off + col0 + c);
+                else { vs[t * DR_COLS + c] = 0.f; vs[t * DR_COLS + c + 1] = 0.f; vs[t * DR_COLS + c + 2] = 0.f; vs[t * DR_COLS + c + 3] = 0.f; }
+            }
+        } else {
+            for (int idx = tid; idx < tt * D.d; idx += blockDim.x) {
+                const int t = idx / D.d, c = idx - t * D.d;
+                const int at = t * RS + c + (c / DPT) * 4;    // the padded place of row c
+                const float* row = qkv + (size_t)(start + t0 + t) * ld;
+                cp_async4(ks + at, row + k_off + c);
+                cp_async4(qs + at, row + q_off + c);
+                if (VEC) cp_async4(gv + at, decay + ((size_t)(start + t0 + t) * D.H + h) * D.d + c);
+            }
+            for (int idx = tid; idx < tt * DR_COLS; idx += blockDim.x) {
+                const int t = idx / DR_COLS, c = idx % DR_COLS;
+                if (col0 + c < D.dv) cp_async4(vs + idx, qkv + (size_t)(start + t0 + t) * ld + v_off + col0 + c);
+                else vs[idx] = 0.f;
+            }
         }
         if (tid < tt) {
             cp_async4(bs + tid, beta + (size_t)(start + t0 + tid) * D.H + h);
@@ -302,6 +324,10 @@ int delta_rule_launch(const Batch& b, const DeltaDims& D, const float* qkv, int 
 #undef DR_ATTR
     }
     const int dpt = (D.d + parts - 1) / parts;
+    {   // 16-byte staging copies when every row the kernel stages starts aligned and has a multiple of 4 entries
+        const int qo = D.q_off >= 0 ? D.q_off : 0, ko = D.k_off >= 0 ? D.k_off : D.Hk * D.d, vo = D.v_off >= 0 ? D.v_off : 2 * D.Hk * D.d;
+        sa.v4 = D.d % 4 == 0 && D.dv % 4 == 0 && ld % 4 == 0 && qo % 4 == 0 && ko % 4 == 0 && vo % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)decay & 15) == 0;
+    }
 #define DR_LAUNCH(dp, pa) delta_rule_kernel<dp, pa, VEC, DELTA><<<grid, DR_THREADS, smem, s>>>(b, D, qkv, ld, beta, decay, state, slot_stride, o, sa)
     if (D.d > 256 || smem > 160 * 1024) { set_error("delta: key dimension %d above the supported 256", D.d); return WF_ERR_UNSUPPORTED; }
     if (decode) { if (dpt <= 8) DR_LAUNCH(8, 4); else if (dpt <= 16) DR_LAUNCH(16, 4); else if (dpt <= 32) DR_LAUNCH(32, 4); else DR_LAUNCH(64, 4); }
