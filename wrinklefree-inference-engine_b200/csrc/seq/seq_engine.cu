@@ -738,7 +738,7 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     auto walloc = [&](void** ptr, size_t count) -> int { return own ? dalloc_t(e, ptr, count) : WF_OK; };
     auto name = [&](const std::string& n, void* dst, size_t count) { if (own) add_tensor(e, n, dst, count); };
     // one mixer: weights named mp + '<tensor>', its part of a cache page, its part of a state slot
-    auto setup_mixer = [&](LayerState& L, const std::string& mp, int index) -> int {
+    auto setup_mixer = [&](LayerState& L, const std::string& mp) -> int {
         const wf_seq_layer& l = L.c;
         int rc = WF_OK;
 #define TRYL(x) do { if ((rc = (x))) return rc; } while (0)
@@ -847,7 +847,6 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
             max_decay = std::max(max_decay, (size_t)L.n_decay);
         }
         max_np = std::max(max_np, (size_t)L.np); max_hv = std::max(max_hv, nv); max_H = std::max(max_H, (size_t)l.heads);
-        (void)index;
 #undef TRYL
         return WF_OK;
     };
@@ -879,13 +878,13 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
                 L.st_canon2 = st; st += (size_t)(taps - 1) * W;
             }
         }
-        TRY(setup_mixer(L, l.pair ? p + "mix.left." : p + "mix.", li));
+        TRY(setup_mixer(L, l.pair ? p + "mix.left." : p + "mix."));
         if (l.pair) {
             LayerState& R = e->layers[l.pair];
             if (!own) R = e->layers[e->layers[l.tied_to].pair_state];
             R.c = layers[l.pair];
             L.pair_state = l.pair;
-            TRY(setup_mixer(R, p + "mix.right.", l.pair));
+            TRY(setup_mixer(R, p + "mix.right."));
         }
         if (l.has_ff == WF_SEQ_FF_DENSE) {
             L.uff = l.ff; L.ulimit = l.ff_limit;
@@ -1019,12 +1018,7 @@ extern "C" int wf_seq_finalize(wf_seq_engine* e) {
     // The bucket of a distance is computed here, once, in double: exact below rel_rows / 2, then logarithmic steps up to rel_far.
     for (int li = 0; li < (int)e->layers.size(); ++li) {
         LayerState& L = e->layers[li];
-        if (L.c.type != WF_SEQ_GQA_ATTENTION || L.c.rel_rows <= 0 || L.c.tied) continue;
-        if (li >= e->cfg.n_layers) {           // a second mixer: skip those whose owner is tied
-            bool tied_owner = false;
-            for (int k = 0; k < e->cfg.n_layers; ++k) if (e->layers[k].c.pair == li && e->layers[k].c.tied) tied_owner = true;
-            if (tied_owner) continue;
-        }
+        if (L.c.type != WF_SEQ_GQA_ATTENTION || L.c.rel_rows <= 0 || L.c.tied) continue;     // a tied layer points at its source's table
         const int B = L.c.rel_rows, H = L.c.heads, half = B / 2;
         std::vector<unsigned char> raw((size_t)B * H * e->esz);
         if (cuda_check(cudaMemcpyAsync(raw.data(), L.rel, raw.size(), cudaMemcpyDeviceToHost, e->stream), "bias table D2H")) return WF_ERR_CUDA;
