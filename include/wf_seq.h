@@ -17,10 +17,13 @@ extern "C" {
 #define WF_SEQ_DELTA 1             /* gated delta rule with short convolutions */
 #define WF_SEQ_GQA_ATTENTION 2     /* grouped-query softmax attention over cached per-head keys and values */
 #define WF_SEQ_SSD 3               /* state-space recurrence with one scalar decay per head (short convolution, gated grouped norm) */
+#define WF_SEQ_MINGRU 4            /* element-wise gated recurrence: gate and candidate read only the current token */
+#define WF_SEQ_MLSTM 5             /* matrix memory with exponential input gate, sigmoid forget gate and a running maximum of the log gates */
 
 /* how a layer wraps its sublayers */
 #define WF_SEQ_BLOCK_SANDWICH 0    /* x += norm_b(sub(conv(norm_a(x)))): grouped norms before and after, input convolution with carried tail */
 #define WF_SEQ_BLOCK_POST 1        /* x += residual_mult * gain * rms(sub(x)): the sublayer reads the stream, ONE gain per norm */
+#define WF_SEQ_BLOCK_PARALLEL 2    /* x += mixer(norm1(x)) + ff(norm2(x)): both branches read the same stream, each behind its own weighted norm */
 
 /* feed-forward kinds (wf_seq_layer.has_ff) and gated activations (ff_act) */
 #define WF_SEQ_FF_NONE 0
@@ -29,6 +32,7 @@ extern "C" {
 #define WF_SEQ_ACT_SILU 0          /* silu(g) * u */
 #define WF_SEQ_ACT_CLAMPED 1       /* g = min(g, limit), u = clamp(u, -limit, limit); g * sigmoid(1.702 g) * (u + 1) */
 #define WF_SEQ_ACT_GELU_TANH 2     /* gelu(g) * u, gelu in its tanh form */
+#define WF_SEQ_ACT_RELU2 3         /* relu(u)^2, no gate: the dense feed-forward has 'mlp.up' and 'mlp.down' only */
 
 /* wf_seq_layer.qk_norm of grouped-query attention */
 #define WF_SEQ_QKNORM_NONE 0
@@ -87,6 +91,28 @@ typedef struct wf_seq_layer {
     /* tied = 1: the layer has no tensors of its own and uses those of layer tied_to (another layer, untied, with the same descriptor;
      * it may come later); its cache rows and its state are its own. */
     int tied, tied_to;
+    /* latent attention, further.  q_rank > 0: queries go through a latent of that size, q = W_uq (w * rms(W_dq x)) (tensors mix.dq,
+     * mix.dq.norm, mix.uq instead of mix.q).  head_gate: 0 = no output gate, otherwise sigmoid(W_g x) per output element.  rope_interleaved
+     * as for grouped-query attention.  sink = 2 (both attention kinds): the softmax denominator carries exp(s_h), s_h a learned number per
+     * head (tensor mix.sink [heads]) that is neither scaled nor given a value.  window: as above; a causal layer passes a window no
+     * sequence reaches. */
+    int q_rank;
+    /* rotation, both attention kinds.  rope_factor > 1: frequency interpolation.  With t(x) = rope_dims * ln(rope_orig / (2 pi x)) /
+     * (2 ln rope_base), lo = max(floor(t(rope_fast)), 0), hi = min(ceil(t(rope_slow)), rope_dims - 1) and ramp_i = clamp((i - lo) /
+     * max(hi - lo, 0.001), 0, 1), pair i turns with f_i / rope_factor * ramp_i + f_i * (1 - ramp_i), f_i = rope_base^(-2i / rope_dims),
+     * and cosines and sines are multiplied by 0.1 ln(rope_factor) + 1.  (The engine tabulates the frequencies once, in double.) */
+    float rope_factor, rope_orig, rope_fast, rope_slow;
+    /* grouped-query attention: v_is_k = 1: there is no value projection; the values are the keys as cached (vdim == dim), and a page
+     * holds the keys only. */
+    int v_is_k;
+    /* WF_SEQ_MINGRU: `vdim` channels (heads = dim = 1).  z = sigmoid(W_z x + b_z), u = W_x x + b_x, c = u + 1/2 (u >= 0) or sigmoid(u);
+     * S <- (1 - z) S + z c per channel; output W_o (S * silu(W_g x)).  Tensors mix.z, mix.z.b, mix.x, mix.x.b, mix.g, mix.o.
+     * WF_SEQ_MLSTM: heads of key size dim and value size vdim.  q = W_q x * dim^-1/2, k, v; per head log gates
+     * i = cap tanh((W_i x + b_i) / cap), f = logsigmoid(cap tanh((W_f x + b_f) / cap)), cap = gate_cap (0: no cap); m <- max(f + m, i)
+     * (m starts at 0); S <- e^(f + m' - m) S + e^(i - m) k v^T, n likewise with k; o = S^T q / (max(|n . q|, e^-m) + 1e-6); each head's o
+     * divided by its root mean square, times mix.norm [heads * vdim], times sigmoid(W_g x), then W_o.  Tensors mix.q, mix.k, mix.v, mix.g,
+     * mix.i, mix.i.b, mix.f, mix.f.b, mix.norm, mix.o. */
+    float gate_cap;
 } wf_seq_layer;
 
 typedef struct wf_seq_config {
@@ -105,6 +131,7 @@ typedef struct wf_seq_config {
     float embed_scale;             /* the embedding row is multiplied by this (0 is read as 1) */
     int norm_weights;              /* WF_SEQ_BLOCK_POST: 1 = the norms have weight vectors of the width instead of a single gain */
     int tied_head;                 /* 1: logits are products with the embedding table itself; there is no 'head' tensor */
+    float norm_offset;             /* added to every stored weight of the layer norms and the final norm (1: weights stored around zero) */
 } wf_seq_config;
 
 typedef struct wf_seq_engine wf_seq_engine;
@@ -144,7 +171,8 @@ int wf_seq_launches_last_step(const wf_seq_engine* e);
  * (float [n_layers, n, width], n = tokens of the step).  wf_seq_run_part runs ONE part of one layer on given float rows (host memory,
  * [n, width]) through the same kernels, caches and state as wf_seq_step, and returns that part's float output [n, width]:
  * 0 first norm, 1 input convolution of the mixer (carried state), 2 the mixer, 3 the feed-forward, 4 input convolution of the
- * feed-forward (1 and 4: WF_SEQ_BLOCK_SANDWICH only; part 0 of WF_SEQ_BLOCK_POST is residual_mult * gain * rms(rows)).
+ * feed-forward (1 and 4: WF_SEQ_BLOCK_SANDWICH only; part 0 of WF_SEQ_BLOCK_POST is residual_mult * gain * rms(rows)), 5 second norm
+ * (WF_SEQ_BLOCK_PARALLEL only).
  * Sequence lengths advance as in a step. */
 int wf_seq_set_layer_tap(wf_seq_engine* e, float* host);
 int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, const int32_t* slots, const int32_t* counts, const float* in_host,

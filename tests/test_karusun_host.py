@@ -193,7 +193,7 @@ def test_sequence_engine_abi_matches_its_header():
         assert name in _lib.SEQ_SYMBOLS, f"{name} has no ctypes signature"
     for name in _lib.SEQ_SYMBOLS:
         assert name in decl or name == "wf_last_error"
-    assert C.sizeof(_lib.SeqLayer) == 49 * 4 and C.sizeof(_lib.SeqConfig) == 19 * 4
+    assert C.sizeof(_lib.SeqLayer) == 56 * 4 and C.sizeof(_lib.SeqConfig) == 20 * 4
     if not torch.cuda.is_available():
         assert L.wf_seq_available() == 0
         from sglang.srt.models.karusun import KarusunForCausalLM

@@ -7,7 +7,7 @@
 // A layer may read the cache rows that an earlier layer wrote instead of projecting its own.
 // Norms, scores, softmax and the weighted sum are float; the cache and the query operand are the storage type.
 //
-// Cache layout of one layer inside a page: keys [G][page_size][d], then values [G][page_size][dv].
+// Cache layout of one layer inside a page: keys [G][page_size][d], then values [G][page_size][dv] (no value part when the values are the keys).
 #include "seq_kernels.cuh"
 #include <math.h>
 
@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(GA_WARPS * 32) gqa_prep_kernel(Batch b, GqaDim
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sq = b.tok_seq[i], pos = b.tok_pos[i];
     const float* row = proj + (size_t)i * ld;
-    const int units = D.H + (k_off >= 0 ? 2 * D.G : 0);
+    const int units = D.H + (k_off >= 0 ? (D.v_is_k ? D.G : 2 * D.G) : 0);      // the values are stored only when they are not the keys
     T* page = nullptr;
     if (k_off >= 0) {
         const int pg = pc.block_table[(size_t)b.seq_slot[sq] * pc.max_blocks + pos / pc.page_size];
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(GA_WARPS * 32) gqa_attn_kernel(Batch b, GqaDim
     const int32_t* bt = pc.block_table + (size_t)b.seq_slot[sq] * pc.max_blocks;
     const float slope = D.dist_exp > 0.f ? exp2f(-D.dist_exp * (float)(h + 1) / (float)D.H) : 0.f;
     const T* qh = qn + ((size_t)i * D.H + h) * D.d;
-    const size_t k_base = (size_t)g * pc.page_size * D.d, v_base = (size_t)D.G * pc.page_size * D.d + (size_t)g * pc.page_size * D.dv;
+    const size_t k_base = (size_t)g * pc.page_size * D.d, v_base = D.v_is_k ? k_base : (size_t)D.G * pc.page_size * D.d + (size_t)g * pc.page_size * D.dv;
     float qreg[GA_MAXD], acc[GA_MAXD];
 #pragma unroll
     for (int t = 0; t < GA_MAXD; ++t) { const int c = lane + 32 * t; qreg[t] = c < D.d ? to_f(qh[c]) : 0.f; acc[t] = 0.f; }
@@ -190,19 +190,20 @@ int check_dims(const GqaDims& D) {
     if (D.d > 32 * GA_MAXD || D.dv > 32 * GA_MAXD) { set_error("attention: per-head sizes %d / %d above the supported %d", D.d, D.dv, 32 * GA_MAXD); return WF_ERR_UNSUPPORTED; }
     if (D.rope_dims < 0 || (D.rope_dims & 1) || D.rope_dims > D.d || D.rope_dims / 2 > GA_MAXROT) { set_error("attention: %d rotated entries of %d", D.rope_dims, D.d); return WF_ERR_INVALID; }
     if (D.qk_norm >= 2 && (!D.q_norm_w || !D.k_norm_w)) { set_error("attention: the query / key norm has no weights"); return WF_ERR_INVALID; }
+    if (D.v_is_k && D.dv != D.d) { set_error("attention: values that are the keys have the keys' size (%d / %d)", D.d, D.dv); return WF_ERR_INVALID; }
     if (D.chunk < 0 || (D.rel && D.rel_n < 1)) { set_error("attention: chunk %d, %d bias rows", D.chunk, D.rel_n); return WF_ERR_INVALID; }
     return WF_OK;
 }
 
 }  // namespace
 
-long long gqa_cache_elems(const GqaDims& D, int page_size) { return (long long)page_size * D.G * (D.d + D.dv); }
+long long gqa_cache_elems(const GqaDims& D, int page_size) { return (long long)page_size * D.G * (D.d + (D.v_is_k ? 0 : D.dv)); }
 
 int launch_gqa_prep(int dt, const Batch& b, const GqaDims& D, const float* proj, int ld, int k_off, int v_off, int g_off, const void* qb, const void* kb,
                     const void* vb, float eps, const PagedCache& pc, void* qn, float* gate, cudaStream_t s) {
     if (b.n <= 0) return WF_OK;
     if (int rc = check_dims(D)) return rc;
-    if ((k_off >= 0) != (v_off >= 0)) { set_error("attention: keys and values are projected together or not at all"); return WF_ERR_INVALID; }
+    if (!D.v_is_k && (k_off >= 0) != (v_off >= 0)) { set_error("attention: keys and values are projected together or not at all"); return WF_ERR_INVALID; }
     if (dt == WF_BF16) gqa_prep_kernel<<<b.n, GA_WARPS * 32, 0, s>>>(b, D, proj, ld, k_off, v_off, g_off, (const __nv_bfloat16*)qb, (const __nv_bfloat16*)kb, (const __nv_bfloat16*)vb, eps, pc, (__nv_bfloat16*)qn, gate);
     else gqa_prep_kernel<<<b.n, GA_WARPS * 32, 0, s>>>(b, D, proj, ld, k_off, v_off, g_off, (const float*)qb, (const float*)kb, (const float*)vb, eps, pc, (float*)qn, gate);
     return launch_check(cudaGetLastError(), "gqa_prep");

@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
                 int slot;
                 const __nv_bfloat16* pg = page_of(ok ? j : 0, slot);
                 am_cp16(kd + (uint32_t)(key * KS + kpart * 8) * 2u, pg + koff + (size_t)slot * D.d, ok && kcol_ok);
-                am_cp16(vd + (uint32_t)(key * VS + vpart * 8) * 2u, pg + voff + (size_t)slot * D.dv, ok && vcol_ok);
+                if (!D.v_is_k) am_cp16(vd + (uint32_t)(key * VS + vpart * 8) * 2u, pg + voff + (size_t)slot * D.dv, ok && vcol_ok);
             }
         } else {
 #pragma unroll
@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(AM_THREADS, 3) gqa_attn_mma_kernel(Batch b, Gq
         if (t + NSTAGE - 1 <= t_hi) stage(t + NSTAGE - 1, (t - t_lo + NSTAGE - 1) % NSTAGE); else am_commit();
         am_wait<NSTAGE - 1>();
         __syncthreads();
-        const uint32_t kb = smem_u32(Ks + (size_t)buf * AM_KT * KS), vb = smem_u32(Vs + (size_t)buf * AM_KT * VS);
+        // values that are the keys are read from the staged key tile itself (same row stride: DKP == DVP then)
+        const uint32_t kb = smem_u32(Ks + (size_t)buf * AM_KT * KS), vb = D.v_is_k ? kb : smem_u32(Vs + (size_t)buf * AM_KT * VS);
         // ---- scores
         float s[NST][4];
 #pragma unroll
@@ -436,7 +437,7 @@ int g_decode_stages = -1;
 
 bool gqa_attn_mma_usable(const GqaDims& D, const PagedCache& pc) {
     const int rep = D.G > 0 ? D.H / D.G : 0;
-    return rep >= 1 && rep <= 16 && D.d % 8 == 0 && D.dv % 8 == 0 && D.d <= 128 && D.dv <= 128 && pc.layer_off % 8 == 0 && pc.page_stride % 8 == 0 &&
+    return rep >= 1 && rep <= 16 && D.d % 8 == 0 && D.dv % 8 == 0 && D.d <= 128 && D.dv <= 128 && (!D.v_is_k || D.d == D.dv) && pc.layer_off % 8 == 0 && pc.page_stride % 8 == 0 &&
            ((long long)pc.page_size * D.d) % 8 == 0 && D.G <= 65535;
 }
 

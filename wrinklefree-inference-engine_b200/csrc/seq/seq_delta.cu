@@ -105,15 +105,16 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
     constexpr int tile_floats = (VEC ? 3 : 2) * DR_TT * RS + DR_TT * DR_COLS + 2 * DR_TT;   // k [TT][RS], q [TT][RS], v [TT][cols], beta [TT], decay [TT], vector decay [TT][RS]
     const int sq = sa.pass ? blockIdx.x / sa.nchunks : blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DR_COLS;
     const int tid = threadIdx.x, p = tid % DR_PARTS, jl = tid / DR_PARTS, col = col0 + jl;
-    const bool col_ok = col < D.dv;
+    const int dvs = D.dv + D.ones_col;                      // state and output columns: the values, and the all-ones column behind them
+    const bool col_ok = col < dvs;
     const int kh = h / (D.H / D.Hk);
     int start = b.seq_start[sq], len = b.seq_len[sq];
-    float* S = state + (size_t)b.seq_slot[sq] * slot_stride + (size_t)h * D.d * D.dv;      // where the state is read ...
+    float* S = state + (size_t)b.seq_slot[sq] * slot_stride + (size_t)h * D.d * dvs;       // where the state is read ...
     float* S_out = S;                                                                        // ... and where it is left
     if (sa.pass) {
         const int c = blockIdx.x - sq * sa.nchunks;
         if (c * sa.chunk >= len) return;                                                     // the whole block: this sequence has fewer chunks
-        const size_t entry = ((size_t)(start / sa.chunk + sq + c) * D.H + h) * D.d * D.dv;
+        const size_t entry = ((size_t)(start / sa.chunk + sq + c) * D.H + h) * D.d * dvs;
         S = sa.pass == 1 ? nullptr : sa.start + entry;
         S_out = sa.pass == 1 ? sa.local + entry : nullptr;
         if (sa.pass == 1 && tid == 0 && blockIdx.z == 0) {                                   // the chunk's decay product (one decay per head)
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
         const int i = p * DPT + m;
-        s[m] = (S && col_ok && i < D.d) ? S[(size_t)i * D.dv + col] : 0.f;
+        s[m] = (S && col_ok && i < D.d) ? S[(size_t)i * dvs + col] : 0.f;
     }
     const int q_off = (D.q_off >= 0 ? D.q_off : 0) + kh * D.d, k_off = (D.k_off >= 0 ? D.k_off : D.Hk * D.d) + kh * D.d,
               v_off = (D.v_off >= 0 ? D.v_off : 2 * D.Hk * D.d) + h * D.dv;
@@ -154,7 +155,10 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
             for (int idx = tid; idx < tt * (DR_COLS / 4); idx += blockDim.x) {
                 const int t = idx / (DR_COLS / 4), c = (idx % (DR_COLS / 4)) << 2;
                 if (col0 + c < D.dv) cp_async16(vs + t * DR_COLS + c, qkv + (size_t)(start + t0 + t) * ld + v_off + col0 + c);
-                else { vs[t * DR_COLS + c] = 0.f; vs[t * DR_COLS + c + 1] = 0.f; vs[t * DR_COLS + c + 2] = 0.f; vs[t * DR_COLS + c + 3] = 0.f; }
+                else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) vs[t * DR_COLS + c + k] = (D.ones_col && col0 + c + k == D.dv) ? 1.f : 0.f;
+                }
             }
         } else {
             for (int idx = tid; idx < tt * D.d; idx += blockDim.x) {
@@ -168,7 +172,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
             for (int idx = tid; idx < tt * DR_COLS; idx += blockDim.x) {
                 const int t = idx / DR_COLS, c = idx % DR_COLS;
                 if (col0 + c < D.dv) cp_async4(vs + idx, qkv + (size_t)(start + t0 + t) * ld + v_off + col0 + c);
-                else vs[idx] = 0.f;
+                else vs[idx] = (D.ones_col && col0 + c == D.dv) ? 1.f : 0.f;
             }
         }
         if (tid < tt) {
@@ -252,14 +256,14 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(Batch b, DeltaDi
             os += __shfl_xor_sync(0xffffffffu, os, 1);
             os += __shfl_xor_sync(0xffffffffu, os, 2);
             if (DR_PARTS == 8) os += __shfl_xor_sync(0xffffffffu, os, 4);
-            if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * D.dv + col] = os;
+            if (p == 0 && col_ok) o[((size_t)(start + t0 + t) * D.H + h) * dvs + col] = os;
         }
     }
     if (!S_out) return;
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
         const int i = p * DPT + m;
-        if (col_ok && i < D.d) S_out[(size_t)i * D.dv + col] = s[m];
+        if (col_ok && i < D.d) S_out[(size_t)i * dvs + col] = s[m];
     }
 }
 
@@ -314,7 +318,7 @@ int delta_rule_launch(const Batch& b, const DeltaDims& D, const float* qkv, int 
                       size_t slot_stride, float* o, cudaStream_t s, ScanArgs sa = ScanArgs()) {
     const bool decode = b.n == b.nseq;                     // every sequence brings one token
     const int parts = decode ? 4 : 8, cols = DR_THREADS / parts;
-    dim3 grid(sa.pass ? b.nseq * sa.nchunks : b.nseq, D.H, (D.dv + cols - 1) / cols);
+    dim3 grid(sa.pass ? b.nseq * sa.nchunks : b.nseq, D.H, (D.dv + D.ones_col + cols - 1) / cols);
     const int dpt_raw = (D.d + parts - 1) / parts, dpt_t = dpt_raw <= 8 ? 8 : (dpt_raw <= 16 ? 16 : (dpt_raw <= 32 ? 32 : 64));
     const size_t smem = 2 * ((size_t)(VEC ? 3 : 2) * DR_TT * parts * (dpt_t + 4) + DR_TT * cols + 2 * DR_TT) * sizeof(float);   // two token groups, padded rows
     static DevOnce once;
@@ -341,6 +345,7 @@ int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int 
                       size_t slot_stride, float* o, cudaStream_t s, const ScanWorkspace* scan) {
     if (b.nseq <= 0) return WF_OK;
     if (D.Hk <= 0 || D.H % D.Hk) { set_error("delta: %d heads over %d key heads", D.H, D.Hk); return WF_ERR_INVALID; }
+    if (D.ones_col && !D.no_delta) { set_error("delta: the all-ones column belongs to the plain recurrence"); return WF_ERR_UNSUPPORTED; }
     if (D.no_delta) {
         if (D.vec_decay) { set_error("delta: the plain recurrence takes one decay per head"); return WF_ERR_UNSUPPORTED; }
         // long portions: chunks in parallel (two short sequential passes instead of one long one)
@@ -350,7 +355,7 @@ int launch_delta_rule(const Batch& b, const DeltaDims& D, const float* qkv, int 
             sa.local = scan->local; sa.start = scan->start; sa.prod = scan->prod;
             sa.pass = 1;
             if (int rc = delta_rule_launch<false, false>(b, D, qkv, ld, beta, decay, state, slot_stride, o, s, sa)) return rc;
-            const int dd = D.d * D.dv;
+            const int dd = D.d * (D.dv + D.ones_col);
             scan_prefix_kernel<<<dim3(b.nseq, D.H, (dd + 255) / 256), 256, 0, s>>>(b, D.H, dd, SCAN_CHUNK, state, slot_stride, scan->local, scan->start, scan->prod);
             if (int rc = launch_check(cudaGetLastError(), "scan_prefix")) return rc;
             sa.pass = 3;

@@ -58,6 +58,16 @@ struct LayerState {
     void *a2 = nullptr, *g2 = nullptr, *conv_b = nullptr, *Dskip = nullptr;
     int g_col = 0, b_col = 0, a_col = 0, n_decay = 0;
     int pair_state = 0;       // index of the second mixer's state in the engine's layer array
+    // latent attention: query latent (norm weight, up-projection), learned sinks as loaded and as floats, rotation frequencies (double
+    // [rope_dims / 2], tabulated at finalize) and the factor on cosines and sines; column of the [latent | rotated key] part in the projection
+    void *dq_norm = nullptr, *uq = nullptr, *sink_raw = nullptr;
+    float* sink_f = nullptr;
+    double* freq = nullptr;
+    float rope_mscale = 1.f;
+    int kv_col = 0;
+    // gated recurrences: the two gate biases (element-wise: z.b, x.b; matrix memory: i.b, f.b); state offset of the running maximum
+    void *gb1 = nullptr, *gb2 = nullptr;
+    size_t st_m = 0;
     // state slot offsets (floats)
     size_t st_canon1 = 0, st_canon2 = 0, st_conv = 0, st_S = 0;
 };
@@ -91,6 +101,10 @@ struct wf_seq_engine {
     void *hperm = nullptr, *h_t = nullptr, *qn = nullptr, *olat = nullptr, *og = nullptr, *hmid = nullptr, *xn = nullptr;
     float *gate = nullptr, *ugu = nullptr, *uy = nullptr;      // head gates; the every-token unit's [gate | up] rows and its output
     float *y2 = nullptr;              // output of the second mixer of a paired layer
+    void* h_t2 = nullptr;             // WF_SEQ_BLOCK_PARALLEL: the feed-forward's input (second norm of the stream)
+    float* qfull = nullptr;           // latent attention with a query latent: the up-projected queries
+    void* cq = nullptr;               // ... and the normalised query latent
+    float* mrun = nullptr;            // matrix memory: running maximum of the log gates per (token, head)
     float *gfull = nullptr, *afull = nullptr;   // recurrences: gate and decay logits when they are products of two matrices
     ScanWorkspace scan;               // state-space recurrence over long portions: per-chunk states (launch_delta_rule)
     void* uhmid = nullptr;
@@ -155,7 +169,7 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
         set_error("wf_seq_create: vocab %d width %d layers %d norm groups %d taps %d", c.vocab, c.width, c.n_layers, c.norm_groups, c.canon_taps);
         return WF_ERR_INVALID;
     }
-    if (c.block_form != WF_SEQ_BLOCK_SANDWICH && c.block_form != WF_SEQ_BLOCK_POST) { set_error("wf_seq_create: block form %d", c.block_form); return WF_ERR_INVALID; }
+    if (c.block_form != WF_SEQ_BLOCK_SANDWICH && c.block_form != WF_SEQ_BLOCK_POST && c.block_form != WF_SEQ_BLOCK_PARALLEL) { set_error("wf_seq_create: block form %d", c.block_form); return WF_ERR_INVALID; }
     if (c.page_size <= 0 || c.max_pages <= 0 || c.slots <= 0 || c.max_step_tokens <= 0) { set_error("wf_seq_create: page / slot / step sizes must be positive"); return WF_ERR_INVALID; }
     if (c.n_extra < 0) { set_error("wf_seq_create: %d extra mixers", c.n_extra); return WF_ERR_INVALID; }
     for (int i = 0; i < c.n_layers + c.n_extra; ++i) {
@@ -175,13 +189,21 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
             }
         }
         if (l.type == WF_SEQ_LATENT_ATTENTION) {
-            if (l.kv_rank <= 0 || l.rot_dim < 0 || l.window < 1 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1)) { set_error("layer %d: latent attention sizes", i); return WF_ERR_INVALID; }
+            if (l.kv_rank <= 0 || l.rot_dim < 0 || l.window < 1 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1) || l.q_rank < 0) { set_error("layer %d: latent attention sizes", i); return WF_ERR_INVALID; }
+            if (l.sink != 0 && l.sink != 2) { set_error("layer %d: latent attention takes no sink or a learned one per head", i); return WF_ERR_INVALID; }
+            if (l.rope_factor < 0.f || (l.rope_factor > 0.f && !(l.rope_orig > 0.f && l.rope_fast > 0.f && l.rope_slow > 0.f && l.rope_base > 1.f))) { set_error("layer %d: frequency interpolation constants", i); return WF_ERR_INVALID; }
+        } else if (l.type == WF_SEQ_MINGRU) {
+            if (l.heads != 1 || l.dim != 1) { set_error("layer %d: the element-wise recurrence has heads = dim = 1 and vdim channels", i); return WF_ERR_INVALID; }
+        } else if (l.type == WF_SEQ_MLSTM) {
+            if (l.gate_cap < 0.f) { set_error("layer %d: gate cap %g", i, l.gate_cap); return WF_ERR_INVALID; }
         } else if (l.type == WF_SEQ_DELTA) {
             if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.conv < 1 || l.decay_rank < 0 || l.gate_rank < 0) { set_error("layer %d: delta sizes", i); return WF_ERR_INVALID; }
         } else if (l.type == WF_SEQ_SSD) {
             if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.conv < 1 || l.out_norm_groups < 1 || (l.heads * l.vdim) % l.out_norm_groups) { set_error("layer %d: state-space sizes", i); return WF_ERR_INVALID; }
         } else if (l.type == WF_SEQ_GQA_ATTENTION) {
             if (l.kv_heads <= 0 || l.heads % l.kv_heads || l.window < 1) { set_error("layer %d: attention sizes", i); return WF_ERR_INVALID; }
+            if (l.v_is_k && (l.vdim != l.dim || l.v_norm || l.kv_from >= 0)) { set_error("layer %d: values that are the keys have the keys' size, no norm of their own and a cache of their own", i); return WF_ERR_INVALID; }
+            if (l.sink < 0 || l.sink > 1) { set_error("layer %d: grouped-query attention takes no sink or the extra one", i); return WF_ERR_INVALID; }
             if (l.qk_norm < 0 || l.qk_norm > 3 || l.rope_dims < 0 || (l.rope_dims & 1) || l.rope_dims > l.dim || l.chunk < 0 || l.rel_rows < 0 || l.softcap < 0.f ||
                 (l.rel_rows > 0 && (l.rel_rows < 2 || !(l.rel_far > (float)(l.rel_rows / 2)))) || l.head_gate < 0 || l.head_gate > 2 || l.proj_bias < 0 || l.proj_bias > 2) {
                 set_error("layer %d: attention options", i); return WF_ERR_INVALID;
@@ -196,7 +218,9 @@ int validate(const wf_seq_config& c, const wf_seq_layer* L) {
         } else { set_error("layer %d: unknown mixer type %d", i, l.type); return WF_ERR_INVALID; }
         if (l.has_ff != WF_SEQ_FF_NONE && l.has_ff != WF_SEQ_FF_ROUTED && l.has_ff != WF_SEQ_FF_DENSE) { set_error("layer %d: feed-forward kind %d", i, l.has_ff); return WF_ERR_INVALID; }
         if (l.has_ff == WF_SEQ_FF_DENSE && l.ff <= 0) { set_error("layer %d: dense feed-forward size", i); return WF_ERR_INVALID; }
-        if (l.has_ff && (l.ff_act < 0 || l.ff_act > 2 || l.shared_ff < 0)) { set_error("layer %d: feed-forward activation / shared size", i); return WF_ERR_INVALID; }
+        if (l.ff_act == WF_SEQ_ACT_RELU2 && l.has_ff != WF_SEQ_FF_DENSE && l.has_ff != WF_SEQ_FF_NONE) { set_error("layer %d: the ungated activation belongs to a dense feed-forward", i); return WF_ERR_INVALID; }
+        if (c.block_form == WF_SEQ_BLOCK_PARALLEL && l.has_ff == WF_SEQ_FF_ROUTED) { set_error("layer %d: the parallel block form takes a dense feed-forward or none", i); return WF_ERR_UNSUPPORTED; }
+        if (l.has_ff && (l.ff_act < 0 || l.ff_act > 3 || l.shared_ff < 0)) { set_error("layer %d: feed-forward activation / shared size", i); return WF_ERR_INVALID; }
         if (l.has_ff == WF_SEQ_FF_ROUTED) {
             const int N = l.experts + l.identity;
             if (l.experts < 0 || l.identity < 0 || N <= 0 || l.top < 1 || l.top > N || l.groups < 1 || N % l.groups || l.keep < 1 || l.keep > l.groups || (l.experts > 0 && l.ff <= 0)) {
@@ -293,11 +317,20 @@ int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     cudaStream_t s = e->stream;
     int rc;
     LatentDims D{H, c.dim, c.rot_dim, c.vdim, c.kv_rank, c.scale, c.rope_base, c.rope_dims, c.window};
+    D.interleaved = c.rope_interleaved; D.freq = L.freq; D.mscale = L.rope_mscale; D.sink = L.sink_f;
     PagedCache pc{e->pool, e->page_stride, L.cache_off, e->cfg.page_size, e->d_block_table, e->pt.max_blocks};
-    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | dkv | g]
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q or its latent | dkv | g]
     mark(e, "latent.proj_gemm");
-    if ((rc = launch_latent_q_prep(e->dt, b, D, e->proj, L.np, e->qn, e->qr, s))) return rc;
-    if ((rc = launch_latent_kv_write(e->dt, b, D, e->proj + nq, L.np, L.dkv_norm, e->cfg.eps, pc, s))) return rc;
+    const float* qsrc = e->proj;
+    int ldq = L.np;
+    if (c.q_rank > 0) {     // the queries' own latent: weighted RMS norm, then the up-projection
+        if ((rc = launch_group_rmsnorm(e->dt, e->proj, L.np, L.dq_norm, 1, e->cfg.eps, n, c.q_rank, nullptr, nullptr, 0, e->cq, c.q_rank, nullptr, s))) return rc;
+        if ((rc = launch_gemm(e->dt, lin(e->cq, 0, c.q_rank, L.uq, c.q_rank, e->qfull, 1, nq, n, nq, c.q_rank), s))) return rc;
+        mark(e, "latent.query_latent");
+        qsrc = e->qfull; ldq = nq;
+    }
+    if ((rc = launch_latent_q_prep(e->dt, b, D, qsrc, ldq, e->qn, e->qr, s))) return rc;
+    if ((rc = launch_latent_kv_write(e->dt, b, D, e->proj + L.kv_col, L.np, L.dkv_norm, e->cfg.eps, pc, s))) return rc;
     mark(e, "latent.q_prep+kv_write");
     {   // qa[i, h, :] = W_uk[h]^T qn[i, h, :]
         GemmArgs g = lin(e->qn, 0, H * c.dim, L.ukT, c.dim, e->qa, 1, H * c.kv_rank, n, c.kv_rank, c.dim);
@@ -331,7 +364,8 @@ int run_latent(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
         if ((rc = launch_gemm(e->dt, g, s))) return rc;
         mark(e, "latent.value_up_gemm");
     }
-    if ((rc = launch_gate_mul(e->dt, e->ov, nv, e->proj + nq + nkv, L.np, 0, n, nv, e->og, nv, s))) return rc;
+    // sigmoid gate per output element, or a plain conversion to the product operand
+    if ((rc = launch_gate_mul(e->dt, e->ov, nv, c.head_gate ? e->proj + L.kv_col + nkv : e->ov, c.head_gate ? L.np : nv, c.head_gate ? 0 : 2, n, nv, e->og, nv, s))) return rc;
     mark(e, "latent.gate");
     rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, out, 1, W, n, W, nv), s);
     mark(e, "latent.out_gemm");
@@ -412,7 +446,7 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     D.rope_dims = c.rope_dims; D.rope_interleaved = c.rope_interleaved; D.rope_base = c.rope_base;
     D.q_norm_w = L.q_norm_w; D.k_norm_w = L.k_norm_w;
     D.chunk = c.chunk; D.sink = c.sink; D.gate_elem = c.head_gate == 2; D.softcap = c.softcap;
-    D.rel = L.rel_dist; D.rel_n = L.rel_n;
+    D.rel = L.rel_dist; D.rel_n = L.rel_n; D.v_is_k = c.v_is_k;
     const LayerState& src = c.kv_from >= 0 ? e->layers[c.kv_from] : L;        // whose cache rows this layer reads
     PagedCache pc{e->pool, e->page_stride, src.cache_off, e->cfg.page_size, e->d_block_table, e->pt.max_blocks};
     if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;     // [q | k | v | g]
@@ -445,8 +479,47 @@ int run_gqa(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     return rc;
 }
 
+// element-wise gated recurrence: [z | x | g] projection -> the recurrence over the portion (gate, candidate, state, silu read-out) -> output
+int run_mingru(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
+    const int W = e->cfg.width, n = b.n, C = L.c.vdim;
+    cudaStream_t s = e->stream;
+    int rc;
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;
+    mark(e, "mingru.proj_gemm");
+    if ((rc = launch_mingru(e->dt, b, C, e->proj, L.np, 0, C, 2 * C, L.gb1, L.gb2, e->state + L.st_S, e->slot_stride, e->og, s))) return rc;
+    mark(e, "mingru.recurrence");
+    rc = launch_gemm(e->dt, lin(e->og, 0, C, L.wo, C, out, 1, W, n, W, C), s);
+    mark(e, "mingru.out_gemm");
+    return rc;
+}
+
+// matrix memory: [q | k | v | g | i | f] projection -> log gates, running maximum, keep / put factors -> the plain decayed outer-product
+// recurrence with the normaliser as one more value column -> division, per-head norm, weight, sigmoid gate -> output
+int run_mlstm(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
+    const wf_seq_layer& c = L.c;
+    const int W = e->cfg.width, n = b.n, H = c.heads, nk = H * c.dim, nv = H * c.vdim;
+    cudaStream_t s = e->stream;
+    int rc;
+    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.wp, W, e->proj, 1, L.np, n, L.np, W), s))) return rc;
+    mark(e, "mlstm.proj_gemm");
+    if ((rc = launch_mlstm_gates(e->dt, b, H, e->proj, L.np, 2 * nk + 2 * nv, 2 * nk + 2 * nv + H, L.gb1, L.gb2, c.gate_cap, e->state + L.st_m, e->slot_stride,
+                                 e->decay, e->beta, e->mrun, s))) return rc;
+    mark(e, "mlstm.gates");
+    DeltaDims D{H, H, c.dim, c.vdim};
+    D.no_delta = 1; D.ones_col = 1; D.q_off = 0; D.k_off = nk; D.v_off = 2 * nk;
+    if ((rc = launch_delta_rule(b, D, e->proj, L.np, e->beta, e->decay, e->state + L.st_S, e->slot_stride, e->od, s, &e->scan))) return rc;
+    mark(e, "mlstm.recurrence");
+    if ((rc = launch_mlstm_post(e->dt, n, H, c.vdim, e->od, e->mrun, 1.f / sqrtf((float)c.dim), L.onorm, e->cfg.eps, e->proj + 2 * nk + nv, L.np, e->og, s))) return rc;
+    mark(e, "mlstm.post");
+    rc = launch_gemm(e->dt, lin(e->og, 0, nv, L.wo, nv, out, 1, W, n, W, nv), s);
+    mark(e, "mlstm.out_gemm");
+    return rc;
+}
+
 int run_one_mixer(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
     switch (L.c.type) {
+        case WF_SEQ_MINGRU: return run_mingru(e, L, b, out);
+        case WF_SEQ_MLSTM: return run_mlstm(e, L, b, out);
         case WF_SEQ_GQA_ATTENTION: return run_gqa(e, L, b, out);
         case WF_SEQ_LATENT_ATTENTION: return run_latent(e, L, b, out);
         case WF_SEQ_SSD: return run_ssd(e, L, b, out);
@@ -468,11 +541,13 @@ int run_mixer(wf_seq_engine* e, LayerState& L, const Batch& b, bool combine = tr
 }
 
 // the gated unit every token runs (dense feed-forward / shared expert): h_t -> out float [n, W]
-int run_unit(wf_seq_engine* e, LayerState& L, const Batch& b, float* out) {
+int run_unit(wf_seq_engine* e, LayerState& L, const Batch& b, float* out, const void* in = nullptr) {
     const int W = e->cfg.width, n = b.n, ff = L.uff;
     cudaStream_t s = e->stream;
     int rc;
-    if ((rc = launch_gemm(e->dt, lin(e->h_t, 0, W, L.ugu, W, e->ugu, 1, 2 * ff, n, 2 * ff, W), s))) return rc;
+    if (!in) in = e->h_t;
+    const int nu = L.c.ff_act == WF_SEQ_ACT_RELU2 ? ff : 2 * ff;       // the ungated activation has no gate half
+    if ((rc = launch_gemm(e->dt, lin(in, 0, W, L.ugu, W, e->ugu, 1, nu, n, nu, W), s))) return rc;
     mark(e, "unit.gate_up");
     if ((rc = launch_silu_mul(e->dt, e->ugu, n, ff, nullptr, e->uhmid, s, L.c.ff_act, L.ulimit))) return rc;
     mark(e, "unit.act");
@@ -607,8 +682,40 @@ int run_layers_post(wf_seq_engine* e, const StepView& v) {
     return WF_OK;
 }
 
+// WF_SEQ_BLOCK_PARALLEL: the mixer and the feed-forward of a layer read the same stream, each through its own weighted norm, and the
+// stream takes the sum of both.  One kernel per layer boundary adds the finished layer's outputs to the stream and forms the next layer's
+// two norm outputs from one pass over the row (the two norms share their statistics).
+int run_layers_parallel(wf_seq_engine* e, const StepView& v) {
+    const int W = e->cfg.width, n = v.b.n, NL = e->cfg.n_layers;
+    const float eps = e->cfg.eps, off = e->cfg.norm_offset;
+    cudaStream_t s = e->stream;
+    int rc;
+    const float escale = e->cfg.embed_scale != 0.f ? e->cfg.embed_scale : 1.f;
+    if ((rc = launch_embed_f32(e->dt, e->embed, v.tokens, n, W, e->x, s, escale))) return rc;
+    mark(e, "embed");
+    {
+        LayerState& L0 = e->layers[0];
+        if ((rc = launch_add_dual_norm(e->dt, e->x, nullptr, 0.f, nullptr, 0.f, nullptr, L0.norm1, L0.c.has_ff ? L0.norm2 : nullptr, off, eps, n, W, e->h_t, e->h_t2, s))) return rc;
+        mark(e, "residual+norms");
+    }
+    for (int li = 0; li < NL; ++li) {
+        LayerState& L = e->layers[li];
+        if ((rc = run_mixer(e, L, v.b, false))) return rc;
+        if (L.c.has_ff && (rc = run_unit(e, L, v.b, e->uy, e->h_t2))) return rc;
+        LayerState* N = li + 1 < NL ? &e->layers[li + 1] : nullptr;
+        if ((rc = launch_add_dual_norm(e->dt, e->x, e->y, L.c.pair ? L.c.mix_scale : 1.f, L.c.pair ? e->y2 : nullptr, L.c.pair_scale, L.c.has_ff ? e->uy : nullptr,
+                                       N ? N->norm1 : nullptr, N && N->c.has_ff ? N->norm2 : nullptr, off, eps, n, W, e->h_t, e->h_t2, s))) return rc;
+        mark(e, "residual+norms");
+        if (e->layer_tap) {
+            if (cuda_check(cudaMemcpyAsync(e->layer_tap + (size_t)li * n * W, e->x, (size_t)n * W * 4, cudaMemcpyDeviceToHost, s), "layer tap")) return WF_ERR_CUDA;
+        }
+    }
+    return WF_OK;
+}
+
 int run_layers(wf_seq_engine* e, const StepView& v) {
     if (e->cfg.block_form == WF_SEQ_BLOCK_POST) return run_layers_post(e, v);
+    if (e->cfg.block_form == WF_SEQ_BLOCK_PARALLEL) return run_layers_parallel(e, v);
     const int W = e->cfg.width, n = v.b.n;
     cudaStream_t s = e->stream;
     int rc;
@@ -650,7 +757,8 @@ int run_head(wf_seq_engine* e, const StepView& v, int nwant) {
     const int W = e->cfg.width;
     int rc;
     if ((rc = ensure_logits(e, nwant))) return rc;
-    if (e->cfg.block_form == WF_SEQ_BLOCK_POST && e->cfg.norm_weights) rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, 1, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
+    if (e->cfg.block_form == WF_SEQ_BLOCK_PARALLEL) rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, 1, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream, nullptr, 1.f, 0.f, e->cfg.norm_offset);
+    else if (e->cfg.block_form == WF_SEQ_BLOCK_POST && e->cfg.norm_weights) rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, 1, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
     else if (e->cfg.block_form == WF_SEQ_BLOCK_POST) rc = launch_scalar_rmsnorm(e->dt, e->x, W, nullptr, e->final_norm, 1.f, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
     else rc = launch_group_rmsnorm(e->dt, e->x, W, e->final_norm, e->cfg.norm_groups, e->cfg.eps, nwant, W, nullptr, nullptr, W, e->xn, W, v.want, e->stream);
     if (rc) return rc;
@@ -721,8 +829,9 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
 #define TRY(x) do { if ((rc = (x))) { wf_seq_destroy(e); return rc; } } while (0)
     if (cuda_check(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking), "stream")) { delete e; return WF_ERR_CUDA; }
     TRY(dalloc_t(e, &e->embed, (size_t)c.vocab * W));
-    const bool post = c.block_form == WF_SEQ_BLOCK_POST;
-    const size_t norm_elems = post && !c.norm_weights ? 1 : W;   // the post form's norms have a single gain unless the model says otherwise
+    const bool parallel = c.block_form == WF_SEQ_BLOCK_PARALLEL;
+    const bool post = c.block_form == WF_SEQ_BLOCK_POST || parallel;       // both have one norm per sublayer and no input convolution
+    const size_t norm_elems = post && !parallel && !c.norm_weights ? 1 : W;   // the post form's norms have a single gain unless the model says otherwise
     TRY(dalloc_t(e, &e->final_norm, norm_elems));
     add_tensor(e, "embed", e->embed, (size_t)c.vocab * W);
     add_tensor(e, "final.norm", e->final_norm, norm_elems);
@@ -733,7 +842,8 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     long long cache_elems = 0;
     size_t st = 0;
     e->layers.resize(c.n_layers + c.n_extra);
-    size_t max_gate = 1, max_decay = 1, max_gfull = 0, max_afull = 0, max_scan = 0;
+    size_t max_gate = 1, max_decay = 1, max_gfull = 0, max_afull = 0, max_scan = 0, max_qfull = 0, max_qrank = 0;
+    bool any_mlstm = false;
     bool own = true;                 // false while a tied layer is laid out: it allocates and names nothing, its weights are its source's
     auto walloc = [&](void** ptr, size_t count) -> int { return own ? dalloc_t(e, ptr, count) : WF_OK; };
     auto name = [&](const std::string& n, void* dst, size_t count) { if (own) add_tensor(e, n, dst, count); };
@@ -749,21 +859,23 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
             const bool ownkv = l.kv_from < 0;
             const size_t ng = l.head_gate == 2 ? nv : (size_t)l.heads;
             size_t off = nq;
-            if (ownkv) { L.k_off = (int)off; off += nk; L.v_off = (int)off; off += nvk; }
+            const bool ownv = ownkv && !l.v_is_k;       // values that are the keys are neither projected nor cached
+            if (ownkv) { L.k_off = (int)off; off += nk; }
+            if (ownv) { L.v_off = (int)off; off += nvk; }
             if (l.head_gate) { L.g_off = (int)off; off += ng; }
             L.np = (int)off;
             TRYL(walloc(&L.wp, (size_t)L.np * W));
             name(mp + "q", L.wp, nq * W);
             if (ownkv) {
                 name(mp + "k", at(e, L.wp, (size_t)L.k_off * W), nk * W);
-                name(mp + "v", at(e, L.wp, (size_t)L.v_off * W), nvk * W);
+                if (ownv) name(mp + "v", at(e, L.wp, (size_t)L.v_off * W), nvk * W);
             }
             if (l.head_gate) name(mp + "g", at(e, L.wp, (size_t)L.g_off * W), ng * W);
             if (l.proj_bias) {
                 TRYL(walloc(&L.qb, nq)); name(mp + "q.b", L.qb, nq);
                 if (ownkv) {
                     TRYL(walloc(&L.kb, nk)); name(mp + "k.b", L.kb, nk);
-                    TRYL(walloc(&L.vb, nvk)); name(mp + "v.b", L.vb, nvk);
+                    if (ownv) { TRYL(walloc(&L.vb, nvk)); name(mp + "v.b", L.vb, nvk); }
                 }
                 if (l.proj_bias == 1) { TRYL(walloc(&L.ob, W)); name(mp + "o.b", L.ob, W); }
             }
@@ -782,17 +894,29 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
                 // every layer's part of a page starts 16-byte aligned
                 cache_elems = (cache_elems + 7) / 8 * 8;
                 L.cache_off = cache_elems;
-                cache_elems += (long long)c.page_size * (nk + nvk);
+                cache_elems += (long long)c.page_size * (nk + (ownv ? nvk : 0));
             }
             max_hd = std::max(max_hd, nq); max_gqa_dv = std::max(max_gqa_dv, (size_t)l.vdim);
             max_gate = std::max(max_gate, ng);
         } else if (l.type == WF_SEQ_LATENT_ATTENTION) {
-            const size_t nq = (size_t)l.heads * (l.dim + l.rot_dim), nkv = l.kv_rank + l.rot_dim;
-            L.np = (int)(nq + nkv + nv);
+            // fused projection [queries, or their latent | latent and rotated key part | gate logits]
+            const size_t nq = (size_t)l.heads * (l.dim + l.rot_dim), nkv = l.kv_rank + l.rot_dim, qcols = l.q_rank > 0 ? (size_t)l.q_rank : nq;
+            L.kv_col = (int)qcols;
+            L.np = (int)(qcols + nkv + (l.head_gate ? nv : 0));
             TRYL(walloc(&L.wp, (size_t)L.np * W));
-            name(mp + "q", L.wp, nq * W);
-            name(mp + "dkv", at(e, L.wp, nq * W), nkv * W);
-            name(mp + "g", at(e, L.wp, (nq + nkv) * W), nv * W);
+            if (l.q_rank > 0) {
+                name(mp + "dq", L.wp, qcols * W);
+                TRYL(walloc(&L.dq_norm, qcols)); name(mp + "dq.norm", L.dq_norm, qcols);
+                TRYL(walloc(&L.uq, nq * qcols)); name(mp + "uq", L.uq, nq * qcols);
+                max_qfull = std::max(max_qfull, nq); max_qrank = std::max(max_qrank, qcols);
+            } else name(mp + "q", L.wp, nq * W);
+            name(mp + "dkv", at(e, L.wp, qcols * W), nkv * W);
+            if (l.head_gate) name(mp + "g", at(e, L.wp, (qcols + nkv) * W), nv * W);
+            if (l.sink == 2) {
+                TRYL(walloc(&L.sink_raw, l.heads)); name(mp + "sink", L.sink_raw, l.heads);
+                if (own) TRYL(dalloc_n(e, &L.sink_f, l.heads));
+            }
+            if (own && l.rope_dims > 0) TRYL(dalloc_n(e, &L.freq, l.rope_dims / 2));
             TRYL(walloc(&L.dkv_norm, l.kv_rank)); name(mp + "dkv.norm", L.dkv_norm, l.kv_rank);
             TRYL(walloc(&L.uk, (size_t)l.heads * l.dim * l.kv_rank)); name(mp + "uk", L.uk, (size_t)l.heads * l.dim * l.kv_rank);
             TRYL(walloc(&L.ukT, (size_t)l.heads * l.dim * l.kv_rank));
@@ -801,6 +925,36 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
             cache_elems += (long long)c.page_size * nkv;
             max_hd = std::max(max_hd, (size_t)l.heads * l.dim); max_hr = std::max(max_hr, (size_t)l.heads * l.kv_rank);
             max_hrot = std::max(max_hrot, (size_t)l.heads * std::max(l.rot_dim, 1));
+        } else if (l.type == WF_SEQ_MINGRU) {
+            // [z | x | g], all of the channel count; state: one float per channel
+            const size_t C = nv;
+            L.np = (int)(3 * C);
+            TRYL(walloc(&L.wp, (size_t)L.np * W));
+            name(mp + "z", L.wp, C * W);
+            name(mp + "x", at(e, L.wp, C * W), C * W);
+            name(mp + "g", at(e, L.wp, 2 * C * W), C * W);
+            TRYL(walloc(&L.gb1, C)); name(mp + "z.b", L.gb1, C);
+            TRYL(walloc(&L.gb2, C)); name(mp + "x.b", L.gb2, C);
+            L.st_S = st; st += C;
+        } else if (l.type == WF_SEQ_MLSTM) {
+            // [q | k | v | g | i | f]; state: the matrix with the normaliser as its last column, then the running maximum per head
+            const size_t nk = (size_t)l.heads * l.dim;
+            L.np = (int)(2 * nk + 2 * nv + 2 * l.heads);
+            TRYL(walloc(&L.wp, (size_t)L.np * W));
+            name(mp + "q", L.wp, nk * W);
+            name(mp + "k", at(e, L.wp, nk * W), nk * W);
+            name(mp + "v", at(e, L.wp, 2 * nk * W), nv * W);
+            name(mp + "g", at(e, L.wp, (2 * nk + nv) * W), nv * W);
+            name(mp + "i", at(e, L.wp, (2 * nk + 2 * nv) * W), (size_t)l.heads * W);
+            name(mp + "f", at(e, L.wp, (2 * nk + 2 * nv + l.heads) * W), (size_t)l.heads * W);
+            TRYL(walloc(&L.gb1, l.heads)); name(mp + "i.b", L.gb1, l.heads);
+            TRYL(walloc(&L.gb2, l.heads)); name(mp + "f.b", L.gb2, l.heads);
+            TRYL(walloc(&L.onorm, nv)); name(mp + "norm", L.onorm, nv);
+            L.st_S = st; st += (size_t)l.heads * l.dim * (l.vdim + 1);
+            L.st_m = st; st += l.heads;
+            max_scan = std::max(max_scan, (size_t)l.heads * l.dim * (l.vdim + 1));
+            max_hv = std::max(max_hv, (size_t)l.heads * (l.vdim + 1));
+            any_mlstm = true;
         } else if (l.type == WF_SEQ_SSD) {
             // [z | x | B | C | dt]: x, B and C are the convolved channels
             const size_t GN = (size_t)l.kv_heads * l.dim;
@@ -888,9 +1042,10 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
         }
         if (l.has_ff == WF_SEQ_FF_DENSE) {
             L.uff = l.ff; L.ulimit = l.ff_limit;
-            TRY(walloc(&L.ugu, (size_t)2 * l.ff * W)); TRY(walloc(&L.ud, (size_t)W * l.ff));
-            name(p + "mlp.gate", L.ugu, (size_t)l.ff * W);
-            name(p + "mlp.up", at(e, L.ugu, (size_t)l.ff * W), (size_t)l.ff * W);
+            const bool gated = l.ff_act != WF_SEQ_ACT_RELU2;
+            TRY(walloc(&L.ugu, (size_t)(gated ? 2 : 1) * l.ff * W)); TRY(walloc(&L.ud, (size_t)W * l.ff));
+            if (gated) name(p + "mlp.gate", L.ugu, (size_t)l.ff * W);
+            name(p + "mlp.up", at(e, L.ugu, gated ? (size_t)l.ff * W : 0), (size_t)l.ff * W);
             name(p + "mlp.down", L.ud, (size_t)W * l.ff);
             max_uff = std::max(max_uff, (size_t)l.ff);
         } else if (l.has_ff == WF_SEQ_FF_ROUTED) {
@@ -947,6 +1102,9 @@ extern "C" int wf_seq_create(const wf_seq_config* cfg, const wf_seq_layer* layer
     if (e->dt == WF_BF16 && max_hr > 1) TRY(dalloc_bytes(e, (void**)&e->attn_ws, (size_t)e->attn_ws_rows * (max_hr + 2 * max_H) * sizeof(float)));
     TRY(dalloc_n(e, &e->gate, (size_t)T * std::max(max_H, max_gate)));
     if (c.n_extra > 0) TRY(dalloc_n(e, &e->y2, (size_t)T * W));
+    if (parallel) TRY(dalloc_t(e, &e->h_t2, (size_t)T * W));
+    if (max_qfull) { TRY(dalloc_n(e, &e->qfull, (size_t)T * max_qfull)); TRY(dalloc_t(e, &e->cq, (size_t)T * max_qrank)); }
+    if (any_mlstm) TRY(dalloc_n(e, &e->mrun, (size_t)T * max_H));
     if (max_scan && T >= 2 * SCAN_CHUNK) {
         e->scan.chunks = scan_chunks_needed(T, c.slots);
         TRY(dalloc_n(e, &e->scan.local, (size_t)e->scan.chunks * max_scan)); TRY(dalloc_n(e, &e->scan.start, (size_t)e->scan.chunks * max_scan));
@@ -1040,6 +1198,47 @@ extern "C" int wf_seq_finalize(wf_seq_engine* e) {
         if (cuda_check(cudaMemcpyAsync(L.rel_dist, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, e->stream), "bias table H2D")) return WF_ERR_CUDA;
         if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;
     }
+    // latent attention: the rotation's frequencies, tabulated in double (with frequency interpolation: pairs whose wavelength is long
+    // against the original context turn `factor` times slower, short ones as they are, a linear ramp over the pair index between), and
+    // the learned sinks as floats
+    for (LayerState& L : e->layers) {
+        if (L.c.type != WF_SEQ_LATENT_ATTENTION || L.c.tied) continue;
+        const wf_seq_layer& l = L.c;
+        if (L.freq) {
+            const int dims = l.rope_dims, half = dims / 2;
+            const double base = l.rope_base, pi = 3.14159265358979323846;
+            std::vector<double> f(half);
+            for (int i = 0; i < half; ++i) f[i] = pow(base, -2.0 * i / dims);
+            L.rope_mscale = 1.f;
+            if (l.rope_factor > 0.f) {
+                const double factor = l.rope_factor;
+                auto pair_of = [&](double turns) { return dims * log((double)l.rope_orig / (2.0 * pi * turns)) / (2.0 * log(base)); };
+                const double lo = std::max(floor(pair_of(l.rope_fast)), 0.0), hi = std::min(ceil(pair_of(l.rope_slow)), (double)(dims - 1));
+                for (int i = 0; i < half; ++i) {
+                    const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+                    f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp);
+                }
+                L.rope_mscale = (float)(0.1 * log(factor) + 1.0);
+            }
+            if (cuda_check(cudaMemcpyAsync(L.freq, f.data(), f.size() * sizeof(double), cudaMemcpyHostToDevice, e->stream), "rotation table H2D")) return WF_ERR_CUDA;
+            if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;
+        }
+        if (L.sink_f) {
+            std::vector<unsigned char> raw((size_t)l.heads * e->esz);
+            if (cuda_check(cudaMemcpyAsync(raw.data(), L.sink_raw, raw.size(), cudaMemcpyDeviceToHost, e->stream), "sinks D2H")) return WF_ERR_CUDA;
+            if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;
+            std::vector<float> sf(l.heads);
+            for (int h = 0; h < l.heads; ++h) {
+                if (e->dt == WF_F32) sf[h] = ((const float*)raw.data())[h];
+                else { const uint32_t bits = (uint32_t)((const uint16_t*)raw.data())[h] << 16; memcpy(&sf[h], &bits, 4); }
+            }
+            if (cuda_check(cudaMemcpyAsync(L.sink_f, sf.data(), sf.size() * 4, cudaMemcpyHostToDevice, e->stream), "sinks H2D")) return WF_ERR_CUDA;
+            if (cuda_check(cudaStreamSynchronize(e->stream), "sync")) return WF_ERR_CUDA;
+        }
+    }
+    // tied latent layers use their source's tables
+    for (LayerState& L : e->layers)
+        if (L.c.type == WF_SEQ_LATENT_ATTENTION && L.c.tied) { const LayerState& S = e->layers[L.c.tied_to]; L.freq = S.freq; L.sink_f = S.sink_f; L.rope_mscale = S.rope_mscale; }
     if (cuda_check(cudaStreamSynchronize(e->stream), "finalize")) return WF_ERR_CUDA;
     e->finalized = true;
     return WF_OK;
@@ -1117,9 +1316,15 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
     cudaStream_t s = e->stream;
     const size_t bytes = (size_t)n * W * 4;
     float* result = e->y;
-    const bool post = e->cfg.block_form == WF_SEQ_BLOCK_POST;
+    const bool parallel = e->cfg.block_form == WF_SEQ_BLOCK_PARALLEL;
+    const bool post = e->cfg.block_form == WF_SEQ_BLOCK_POST || parallel;
+    if (part == 5 && !(parallel && L.c.has_ff)) { set_error("wf_seq_run_part: layer %d has no second norm", layer); return WF_ERR_INVALID; }
     if (post && (part == 1 || part == 4)) { set_error("wf_seq_run_part: this model's sublayers have no input convolution"); return WF_ERR_INVALID; }
-    if (part == 0 && post && e->cfg.norm_weights) {
+    if ((part == 0 || part == 5) && parallel) {
+        if (cuda_check(cudaMemcpyAsync(e->x, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
+        rc = launch_group_rmsnorm(e->dt, e->x, W, part == 0 ? L.norm1 : L.norm2, 1, e->cfg.eps, n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s, nullptr, 1.f, 0.f, e->cfg.norm_offset);
+        result = e->hn;
+    } else if (part == 0 && post && e->cfg.norm_weights) {
         if (cuda_check(cudaMemcpyAsync(e->x, in_host, bytes, cudaMemcpyHostToDevice, s), "in")) return WF_ERR_CUDA;
         rc = launch_group_rmsnorm(e->dt, e->x, W, L.norm1, 1, e->cfg.eps, n, W, nullptr, e->hn, W, nullptr, 0, nullptr, s);
         result = e->hn;
@@ -1145,7 +1350,7 @@ extern "C" int wf_seq_run_part(wf_seq_engine* e, int layer, int part, int nseq, 
         if (post && cuda_check(cudaMemcpyAsync(e->x, e->hn, bytes, cudaMemcpyDeviceToDevice, s), "in")) return WF_ERR_CUDA;
         rc = launch_gate_mul(e->dt, e->hn, W, e->hn, W, 2, n, W, e->h_t, W, s);
         if (!rc) rc = part == 2 ? run_mixer(e, L, v.b) : run_ff(e, L, v.b);
-        if (!rc && part == 2 && L.ob && post && !e->cfg.norm_weights && !L.c.pair) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
+        if (!rc && part == 2 && L.ob && post && !parallel && !e->cfg.norm_weights && !L.c.pair) rc = launch_add_bias(e->dt, e->y, W, L.ob, n, W, s);
     } else { set_error("wf_seq_run_part: unknown part %d", part); return WF_ERR_INVALID; }
     if (rc) return rc;
     if (cuda_check(cudaMemcpyAsync(out_host, result, bytes, cudaMemcpyDeviceToHost, s), "out")) return WF_ERR_CUDA;

@@ -15,9 +15,15 @@ int launch_embed_f32(int dt, const void* table, const int32_t* tokens, int n, in
 int launch_axpby(float* y, float a, const float* y2, float b, size_t count, cudaStream_t s);
 // y = [res +] w * x / sqrt(mean_g(x^2) + eps) per row and per group of W / groups consecutive elements.  x, y, res float [n, W] with row
 // strides ldx / ldy (res shares ldy; y may alias res); rows: optional gather of the input AND residual rows.  y_t: optional T copy of y.
-// x2 (optional, same layout as x): the input is a * x + b * x2.
+// x2 (optional, same layout as x): the input is a * x + b * x2.  w_offset is added to every weight (1: weights stored around zero).
 int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
-                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s, const float* x2 = nullptr, float a = 1.f, float b = 0.f);
+                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s, const float* x2 = nullptr, float a = 1.f, float b = 0.f,
+                         float w_offset = 0.f);
+// The stream update and the input norms of a layer whose two branches read the same stream, in one kernel:
+// x += (a1 * y1 + a2 * y2) + y3 (each term optional; x, y* float [n, W] dense), then with r = x / sqrt(mean(x^2) + eps):
+// h1 = r * (w_offset + w1), h2 = r * (w_offset + w2) as T [n, W] (each optional: null weights).  The row statistics are formed once.
+int launch_add_dual_norm(int dt, float* x, const float* y1, float a1, const float* y2, float a2, const float* y3, const void* w1, const void* w2,
+                         float w_offset, float eps, int n, int W, void* h1, void* h2, cudaStream_t s);
 // x[i, :] = table[tokens[i], :] + sinusoidal position vector of tok_pos[i] (entry 2k sin, 2k + 1 cos of pos * base^(-2k / W)); x_t: optional T copy
 int launch_embed_pos(int dt, const void* table, const int32_t* tokens, const int32_t* tok_pos, int n, int W, float base, float* x, void* x_t, cudaStream_t s);
 // x_t T [n, W] = x float [n, W] rounded to the storage type (dense rows)
@@ -78,7 +84,12 @@ bool gemv_pairs_usable(int dt, const GemmArgs& g);
 int launch_gemv_pairs(int dt, const GemmArgs& g, const int32_t* pair_expert, int n_experts, int pairs, int pair_div, cudaStream_t s);
 
 // ---- latent attention ---------------------------------------------------------------------------------------------------
-struct LatentDims { int H, d, r, dv, R; float scale, rope_base; int rope_dims, window; };
+// interleaved: rotated pairs are (2i, 2i + 1) instead of (i, i + rope_dims / 2).  freq (device, double [rope_dims / 2]): the pairs'
+// frequencies, tabulated by the caller (null: rope_base^(-2i / rope_dims) in float); the angle pos * freq, its cosine and sine are then
+// formed in double and rounded once; mscale multiplies cosines and sines.  sink (device, float [H]): the softmax denominator carries
+// exp(sink[h]) (null: nothing).
+struct LatentDims { int H, d, r, dv, R; float scale, rope_base; int rope_dims, window;
+                    int interleaved = 0; const double* freq = nullptr; float mscale = 1.f; const float* sink = nullptr; };
 // q float [n, H * (d + r)] (ldq): unrotated parts -> qn T [n, H, d]; rotated parts -> rotary at tok_pos -> qr float [n, H, r]
 int launch_latent_q_prep(int dt, const Batch& b, const LatentDims& L, const float* q, int ldq, void* qn, float* qr, cudaStream_t s);
 // dkv float [n, R + r] (ld): first R RMS-normed with weight w (plain), last r rotated; written as T into the paged cache row of
@@ -119,6 +130,7 @@ struct GqaDims {
     const void *q_norm_w = nullptr, *k_norm_w = nullptr;
     int chunk = 0, sink = 0, gate_elem = 0; float softcap = 0.f;
     const float* rel = nullptr; int rel_n = 0;
+    int v_is_k = 0;               // the values are the cached keys (dv == d): a page holds keys only, nothing is projected or stored for values
 };
 // elements one layer's keys and values take in a cache page: keys [G][page_size][d], then values [G][page_size][dv]
 long long gqa_cache_elems(const GqaDims& D, int page_size);
@@ -145,7 +157,9 @@ int launch_gqa_attn_mma(const Batch& b, const GqaDims& D, const void* qn, const 
 // vec_decay: the decay has one entry per head and key channel ([n, H, d]) instead of one per head.  q_off / k_off / v_off: columns of the
 // first query head, key head and value head in a row (negative: the layout [q heads | k heads | v heads]).  no_delta: the write is
 // u = beta v (a plain decayed outer-product accumulation: the state-space recurrence) instead of u = beta (v - S^T k).
-struct DeltaDims { int H, Hk, d, dv; int vec_decay = 0, no_delta = 0, q_off = -1, k_off = -1, v_off = -1; };
+// ones_col (no_delta form): the state has one more column whose value input is 1 for every token, so that column dv of the output is
+// n . q with n the decayed sum of the written keys; state [H][d][dv + 1] and o [n, H, dv + 1] then.
+struct DeltaDims { int H, Hk, d, dv; int vec_decay = 0, no_delta = 0, q_off = -1, k_off = -1, v_off = -1, ones_col = 0; };
 // in place on qkv float [n, C = 2 * Hk * d + H * dv] (ld): q and k heads -> unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.
 // beta[n, H] = sigmoid(b_raw), decay[n, H] = exp(-exp(A_log[h]) * softplus(a_raw + dt_bias[h]))   (a_raw, b_raw float with strides);
 // with D.vec_decay a_raw and dt_bias have H * d entries and decay is [n, H, d]
@@ -169,6 +183,23 @@ int launch_ssd_prep(int dt, int n, int H, const float* dt_raw, int ld, const voi
 int launch_ssd_post(int dt, int n, int H, int dv, int groups, const float* o, const float* x, int ldx, const float* z, int ldz, const void* Dskip,
                     const void* w, float eps, void* y, cudaStream_t s);
 
+// ---- gated recurrences (seq_gated.cu) ------------------------------------------------------------------------------------------
+// element-wise gated recurrence over C channels: z = sigmoid(proj[z_off + c] + zb[c]), u = proj[x_off + c] + xb[c], cand = u + 1/2 where
+// u >= 0 else sigmoid(u); S <- (1 - z) S + z cand (state float [slot][C], carried); out T [n, C] = S * silu(proj[g_off + c]).
+// Long portions are cut into time slices that run in parallel inside a block (the recurrence is linear in S).
+int launch_mingru(int dt, const Batch& b, int C, const float* proj, int ld, int z_off, int x_off, int g_off, const void* zb, const void* xb,
+                  float* state, size_t slot_stride, void* out, cudaStream_t s);
+// log gates of the matrix memory and their running maximum, per (sequence, head) in token order (a warp scans 32 tokens at a time):
+// li = cap tanh((proj[i_off + h] + ib[h]) / cap), lf = logsigmoid(cap tanh((proj[f_off + h] + fb[h]) / cap)) (cap <= 0: no cap);
+// m_t = max(lf + m_(t-1), li) with m carried in mstate[slot * slot_stride + h]; keep[n, H] = exp(lf + m_(t-1) - m_t),
+// put[n, H] = exp(li - m_t), mrun[n, H] = m_t.
+int launch_mlstm_gates(int dt, const Batch& b, int H, const float* proj, int ld, int i_off, int f_off, const void* ib, const void* fb, float cap,
+                       float* mstate, size_t slot_stride, float* keep, float* put, float* mrun, cudaStream_t s);
+// read-out of the matrix memory: o float [n, H, dv + 1] (column dv = n . q) -> per head o * qscale / (max(|n . q| * qscale, exp(-m)) + 1e-6),
+// divided by its root mean square (eps), times w[H * dv], times sigmoid(g float [n, H * dv] (ldg)) -> y T [n, H * dv]
+int launch_mlstm_post(int dt, int n, int H, int dv, const float* o, const float* mrun, float qscale, const void* w, float eps, const float* g, int ldg,
+                      void* y, cudaStream_t s);
+
 // ---- routed feed-forward ---------------------------------------------------------------------------------------------------
 struct RouterDims {
     int E, I, top, groups, keep;   // E real experts, I identity experts (indices E .. E + I - 1)
@@ -191,7 +222,8 @@ int launch_router_fused(int dt, const RouterDims& R, int n, const float* x, int 
 int launch_moe_plan(const RouterDims& R, int n, const int32_t* ids, const int32_t* counts, int32_t* scratch, int32_t* sorted_rows,
                     int32_t* pair_row, int32_t* tile_group, int P, cudaStream_t s);
 // hmid T [P, ff] = act(gu[:, :ff], gu[:, ff:])   (gu float [P, 2 ff]); rows of skipped tiles are left alone (tile_group null: every row).
-// act 0: silu(g) * u;  act 1: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(1.702 g) * (u + 1);  act 2: gelu(g) * u (tanh form)
+// act 0: silu(g) * u;  act 1: g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(1.702 g) * (u + 1);  act 2: gelu(g) * u (tanh form);
+// act 3: relu(u)^2 with gu float [P, ff] (no gate half)
 int launch_silu_mul(int dt, const float* gu, int P, int ff, const int32_t* tile_group, void* hmid, cudaStream_t s, int act = 0, float limit = 0.f);
 // out float [n, W] = sum_k wts[t, k] * (ids[t, k] < E ? y[pair_row[t, k], :] : h[t, :])     (h T [n, W]; pair_row null: row t * top + k)
 // shared_y (optional, float [n, W]): a shared expert's output, added times sigmoid(shared_gate[i * ld_gate]) (shared_gate null: times 1)

@@ -2,7 +2,9 @@
 // Per head the key is k_j = [W_uk c_j, kr_j] and the value W_uv c_j; neither is ever materialised: the query's unrotated part is carried
 // through the key up-projection once (qa = W_uk^T q, a per-head batched product done by the caller), scores are qa . c_j + qr . kr_j, the
 // weighted sum runs over the latents and the value up-projection is applied to that sum (again a batched product).  Scores, softmax and
-// the weighted sum are float.
+// the weighted sum are float.  The rotated parts turn in pairs (i, i + dims / 2) or (2i, 2i + 1); with a frequency table (interpolated
+// frequencies, tabulated once by the engine) the angle, cosine and sine of a pair are formed in double, once per token, and rounded once.
+// A learned per-head sink adds exp(sink_h) to the softmax denominator.
 #include "seq_kernels.cuh"
 #include <math.h>
 
@@ -11,34 +13,47 @@ namespace seq {
 
 namespace {
 
-// pair (i, i + dims / 2) of a vector at position pos: angle pos * base^(-2 i / dims), all in float
-__device__ __forceinline__ void rope_pair(float u, float v, int i, int dims, float base, int pos, float* ou, float* ov) {
-    const float f = powf(base, -2.0f * (float)i / (float)dims);
-    const float a = (float)pos * f;
-    float sn, cs;
-    sincosf(a, &sn, &cs);
-    *ou = u * cs - v * sn;
-    *ov = v * cs + u * sn;
+constexpr int LA_MAXPAIRS = 128;   // rotated pairs of a head
+
+// cosines and sines of one token's pairs into shared memory (the caller synchronises): from the frequency table in double, or from the
+// base in float
+__device__ __forceinline__ void rope_table(const LatentDims& L, int pos, float* cs, float* sn) {
+    const int half = L.rope_dims / 2;
+    for (int p = threadIdx.x; p < half; p += blockDim.x) {
+        if (L.freq) {
+            const double a = (double)pos * L.freq[p];
+            cs[p] = (float)cos(a) * L.mscale; sn[p] = (float)sin(a) * L.mscale;
+        } else {
+            const float a = (float)pos * powf(L.rope_base, -2.0f * (float)p / (float)L.rope_dims);
+            float s_, c_;
+            sincosf(a, &s_, &c_);
+            cs[p] = c_ * L.mscale; sn[p] = s_ * L.mscale;
+        }
+    }
+}
+// entry e of a rotated part `src` (r entries, the first rope_dims of them in pairs) after the rotation
+__device__ __forceinline__ float rope_entry(const LatentDims& L, const float* __restrict__ src, int e, const float* cs, const float* sn) {
+    if (e >= L.rope_dims) return src[e];
+    const int half = L.rope_dims / 2;
+    int p, other; bool first;
+    if (L.interleaved) { p = e >> 1; other = e ^ 1; first = !(e & 1); }
+    else { first = e < half; p = first ? e : e - half; other = first ? e + half : e - half; }
+    return first ? src[e] * cs[p] - src[other] * sn[p] : src[e] * cs[p] + src[other] * sn[p];
 }
 
 template <typename T>
 __global__ void latent_q_prep_kernel(Batch b, LatentDims L, const float* __restrict__ q, int ldq, T* __restrict__ qn, float* __restrict__ qr) {
+    __shared__ float cs[LA_MAXPAIRS], sn[LA_MAXPAIRS];
     const int i = blockIdx.x;
     const int pos = b.tok_pos[i];
-    const int per = L.d + L.r, half = L.rope_dims / 2;
+    const int per = L.d + L.r;
+    rope_table(L, pos, cs, sn);
+    __syncthreads();
     for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < L.H * per; idx += gridDim.y * blockDim.x) {
         const int h = idx / per, c = idx % per;
         const float* src = q + (size_t)i * ldq + (size_t)h * per;
         if (c < L.d) { qn[((size_t)i * L.H + h) * L.d + c] = from_f<T>(src[c]); continue; }
-        const int e = c - L.d;
-        float* dst = qr + ((size_t)i * L.H + h) * L.r;
-        if (e < half) {
-            float ou, ov;
-            rope_pair(src[L.d + e], src[L.d + e + half], e, L.rope_dims, L.rope_base, pos, &ou, &ov);
-            dst[e] = ou; dst[e + half] = ov;
-        } else if (e >= L.rope_dims) {
-            dst[e] = src[c];
-        }
+        qr[((size_t)i * L.H + h) * L.r + c - L.d] = rope_entry(L, src + L.d, c - L.d, cs, sn);
     }
 }
 
@@ -46,8 +61,10 @@ __global__ void latent_q_prep_kernel(Batch b, LatentDims L, const float* __restr
 template <typename T>
 __global__ void latent_kv_write_kernel(Batch b, LatentDims L, const float* __restrict__ dkv, int ld, const T* __restrict__ w, float eps, PagedCache pc) {
     __shared__ float scratch[33];
+    __shared__ float cs[LA_MAXPAIRS], sn[LA_MAXPAIRS];
     const int i = blockIdx.x;
     const int sq = b.tok_seq[i], pos = b.tok_pos[i];
+    rope_table(L, pos, cs, sn);
     const int page = pc.block_table[(size_t)b.seq_slot[sq] * pc.max_blocks + pos / pc.page_size];
     T* row = (T*)pc.pool + (size_t)page * pc.page_stride + pc.layer_off + (size_t)(pos % pc.page_size) * (L.R + L.r);
     const float* src = dkv + (size_t)i * ld;
@@ -56,16 +73,8 @@ __global__ void latent_kv_write_kernel(Batch b, LatentDims L, const float* __res
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)L.R + eps);
     for (int c = threadIdx.x; c < L.R; c += blockDim.x) row[c] = from_f<T>(src[c] * inv * to_f(w[c]));
-    const int half = L.rope_dims / 2;
-    for (int e = threadIdx.x; e < L.r; e += blockDim.x) {
-        if (e < half) {
-            float ou, ov;
-            rope_pair(src[L.R + e], src[L.R + e + half], e, L.rope_dims, L.rope_base, pos, &ou, &ov);
-            row[L.R + e] = from_f<T>(ou); row[L.R + e + half] = from_f<T>(ov);
-        } else if (e >= L.rope_dims) {
-            row[L.R + e] = from_f<T>(src[L.R + e]);
-        }
-    }
+    // (block_sum has synchronised the block since the table was written)
+    for (int e = threadIdx.x; e < L.r; e += blockDim.x) row[L.R + e] = from_f<T>(rope_entry(L, src + L.R, e, cs, sn));
 }
 
 constexpr int LA_WARPS = 4;
@@ -131,6 +140,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(Batch b, Lat
     float lg = 0.f, sc_w[LA_WARPS];
 #pragma unroll
     for (int w = 0; w < LA_WARPS; ++w) { sc_w[w] = part_m[w] == -INFINITY ? 0.f : expf(part_m[w] - mg); lg += part_l[w] * sc_w[w]; }
+    if (L.sink) lg += expf(L.sink[h] - mg);      // the sink: a weight without a value
     const float inv = 1.f / lg;
     for (int c = threadIdx.x; c < L.R; c += blockDim.x) {
         float v = 0.f;
@@ -142,6 +152,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(Batch b, Lat
 
 int check_dims(const LatentDims& L) {
     if (L.R > 32 * LA_MAXR || L.r > 32 * LA_MAXr) { set_error("latent attention: kv_rank %d / rot_dim %d above the supported %d / %d", L.R, L.r, 32 * LA_MAXR, 32 * LA_MAXr); return WF_ERR_UNSUPPORTED; }
+    if (L.rope_dims / 2 > LA_MAXPAIRS) { set_error("latent attention: %d rotated pairs above the supported %d", L.rope_dims / 2, LA_MAXPAIRS); return WF_ERR_UNSUPPORTED; }
     if (L.rope_dims > L.r || (L.rope_dims & 1) || L.window < 1) { set_error("latent attention: rotary dims %d of %d, window %d", L.rope_dims, L.r, L.window); return WF_ERR_INVALID; }
     return WF_OK;
 }

@@ -202,7 +202,7 @@ __global__ void latent_attn_mma_kernel(Batch b, LatentDims L, const float* __res
         if (h >= L.H) continue;
         const float lsum = ssum[(ht * 4 + 0) * 16 + r] + ssum[(ht * 4 + 1) * 16 + r] + ssum[(ht * 4 + 2) * 16 + r] + ssum[(ht * 4 + 3) * 16 + r];
         if (mp.splits == 1) {
-            const float inv = 1.f / lsum;
+            const float inv = 1.f / (L.sink ? lsum + expf(L.sink[h] - m_run[h2]) : lsum);      // the sink: a weight without a value
             __nv_bfloat16* dst = out + ((size_t)i * L.H + h) * L.R + w4 * NT * 8 + cq;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
@@ -217,7 +217,7 @@ __global__ void latent_attn_mma_kernel(Batch b, LatentDims L, const float* __res
 }
 
 // one block per (token, head): out = sum_s exp(m_s - m) O_s / sum_s exp(m_s - m) l_s
-__global__ void latent_attn_merge_kernel(int H, int R, int splits, const float* __restrict__ part, __nv_bfloat16* __restrict__ out) {
+__global__ void latent_attn_merge_kernel(int H, int R, int splits, const float* __restrict__ part, __nv_bfloat16* __restrict__ out, const float* __restrict__ sink) {
     const int i = blockIdx.x, h = blockIdx.y;
     const float* p0 = part + (((size_t)i * splits) * H + h) * (R + 2);
     const size_t sstride = (size_t)H * (R + 2);
@@ -225,6 +225,7 @@ __global__ void latent_attn_merge_kernel(int H, int R, int splits, const float* 
     for (int s = 0; s < splits; ++s) m = fmaxf(m, p0[s * sstride + R]);
     float l = 0.f;
     for (int s = 0; s < splits; ++s) { const float ms = p0[s * sstride + R]; if (ms != -INFINITY) l += expf(ms - m) * p0[s * sstride + R + 1]; }
+    if (sink) l += expf(sink[h] - m);
     const float inv = 1.f / l;
     for (int c = threadIdx.x; c < R; c += blockDim.x) {
         float v = 0.f;
@@ -438,7 +439,12 @@ __global__ void __launch_bounds__(256) latent_attn_kt_kernel(Batch b, LatentDims
     __syncthreads();
     if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < NH; ++k) { ml_s[warp + 8 * k] = m_run[k]; ml_s[HP + warp + 8 * k] = l_run[k]; }
+        for (int k = 0; k < NH; ++k) {
+            const int h = warp + 8 * k;
+            ml_s[h] = m_run[k];
+            // an unsplit key range normalises here, so the sink (a weight without a value) joins the sum here; key splits leave it to the merge
+            ml_s[HP + h] = (L.sink && mp.splits == 1 && h < L.H) ? l_run[k] + expf(L.sink[h] - m_run[k]) : l_run[k];
+        }
     }
     __syncthreads();
 #pragma unroll
@@ -523,7 +529,7 @@ int launch_latent_attn_kt(const Batch& b, const LatentDims& L, const float* qa, 
     if (rc) return rc;
     if (mp.splits > 1) {
         dim3 grid(b.n, L.H);
-        latent_attn_merge_kernel<<<grid, 128, 0, s>>>(L.H, L.R, mp.splits, workspace, (__nv_bfloat16*)out);
+        latent_attn_merge_kernel<<<grid, 128, 0, s>>>(L.H, L.R, mp.splits, workspace, (__nv_bfloat16*)out, L.sink);
         return launch_check(cudaGetLastError(), "latent_attn_merge");
     }
     return WF_OK;
@@ -573,7 +579,7 @@ int launch_latent_attn_mma(const Batch& b, const LatentDims& L, const float* qa,
     if (rc) return rc;
     if (mp.splits > 1) {
         dim3 grid(b.n, L.H);
-        latent_attn_merge_kernel<<<grid, 128, 0, s>>>(L.H, L.R, mp.splits, workspace, (__nv_bfloat16*)out);
+        latent_attn_merge_kernel<<<grid, 128, 0, s>>>(L.H, L.R, mp.splits, workspace, (__nv_bfloat16*)out, L.sink);
         return launch_check(cudaGetLastError(), "latent_attn_merge");
     }
     return WF_OK;

@@ -194,9 +194,14 @@ template <typename T, int VEC>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int ff, const int32_t* __restrict__ tile_group, T* __restrict__ hmid, int act, float limit) {
     const int r = blockIdx.x;
     if (tile_group && tile_group[r / GEMM_BM] < 0) return;
-    const float* row = gu + (size_t)r * 2 * ff;
+    const float* row = gu + (size_t)r * (act == 3 ? 1 : 2) * ff;
     for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC; c < ff; c += gridDim.y * blockDim.x * VEC) {
         float g[VEC], u[VEC];
+        if (act == 3) {                   // no gate half: relu(u)^2
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) { const float z = fmaxf(row[c + v], 0.f); hmid[(size_t)r * ff + c + v] = from_f<T>(z * z); }
+            continue;
+        }
         if (VEC == 4) {
             const float4 a = *reinterpret_cast<const float4*>(row + c), b = *reinterpret_cast<const float4*>(row + ff + c);
             g[0] = a.x; g[1 % VEC] = a.y; g[2 % VEC] = a.z; g[3 % VEC] = a.w;

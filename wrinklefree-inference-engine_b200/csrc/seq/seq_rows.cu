@@ -137,7 +137,7 @@ int launch_add_bias(int dt, float* y, int ld, const void* bias, int n, int W, cu
 template <typename T>
 __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const T* __restrict__ w, int gw, float eps, const float* res,
                                      float* y, int ldy, T* __restrict__ y_t, int ldt, const int32_t* __restrict__ rows, const float* __restrict__ x2, float a,
-                                     float b) {
+                                     float b, float w_offset) {
     __shared__ float scratch[33];
     const int i = blockIdx.x, g = blockIdx.y;
     const int src = rows ? rows[i] : i;
@@ -148,7 +148,7 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)gw + eps);
     for (int c = threadIdx.x; c < gw; c += blockDim.x) {
-        float v = (xr2 ? a * xr[c] + b * xr2[c] : xr[c]) * inv * to_f(w[g * gw + c]);
+        float v = (xr2 ? a * xr[c] + b * xr2[c] : xr[c]) * inv * (w_offset + to_f(w[g * gw + c]));
         if (res) v += res[(size_t)src * ldy + g * gw + c];
         if (y) y[(size_t)i * ldy + g * gw + c] = v;
         if (y_t) y_t[(size_t)i * ldt + g * gw + c] = from_f<T>(v);
@@ -156,16 +156,61 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const
 }
 
 int launch_group_rmsnorm(int dt, const float* x, int ldx, const void* w, int groups, float eps, int n, int W, const float* res, float* y,
-                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s, const float* x2, float a, float b) {
+                         int ldy, void* y_t, int ldt, const int32_t* rows, cudaStream_t s, const float* x2, float a, float b, float w_offset) {
     if (n <= 0) return WF_OK;
     if (groups <= 0 || W % groups) { set_error("group_rmsnorm: width %d not divisible into %d groups", W, groups); return WF_ERR_INVALID; }
     if (res && rows && y == res) { set_error("group_rmsnorm: gathered rows cannot be added in place"); return WF_ERR_INVALID; }
     const int gw = W / groups;
     const int threads = gw >= 2048 ? 512 : (gw >= 1024 ? 256 : (gw >= 256 ? 128 : 64));
     dim3 grid(n, groups);
-    if (dt == WF_BF16) group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const __nv_bfloat16*)w, gw, eps, res, y, ldy, (__nv_bfloat16*)y_t, ldt, rows, x2, a, b);
-    else group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const float*)w, gw, eps, res, y, ldy, (float*)y_t, ldt, rows, x2, a, b);
+    if (dt == WF_BF16) group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const __nv_bfloat16*)w, gw, eps, res, y, ldy, (__nv_bfloat16*)y_t, ldt, rows, x2, a, b, w_offset);
+    else group_rmsnorm_kernel<<<grid, threads, 0, s>>>(x, ldx, (const float*)w, gw, eps, res, y, ldy, (float*)y_t, ldt, rows, x2, a, b, w_offset);
     return launch_check(cudaGetLastError(), "group_rmsnorm");
+}
+
+// One block per row; the updated row stays in registers between the sum of squares and the two scaled copies (up to AD_PER elements per
+// thread; wider rows are re-read from x, which the same thread has just written).
+constexpr int AD_THREADS = 256, AD_PER = 8;
+template <typename T>
+__global__ void __launch_bounds__(AD_THREADS) add_dual_norm_kernel(float* __restrict__ x, const float* __restrict__ y1, float a1, const float* __restrict__ y2, float a2,
+                                                                     const float* __restrict__ y3, const T* __restrict__ w1, const T* __restrict__ w2, float w_offset,
+                                                                     float eps, int W, T* __restrict__ h1, T* __restrict__ h2) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * W;
+    const bool adds = y1 || y2 || y3;
+    float keep[AD_PER];
+    float ss = 0.f;
+    int k = 0;
+    for (int c = threadIdx.x; c < W; c += AD_THREADS, ++k) {
+        float v = x[base + c];
+        if (adds) {
+            float t = 0.f;
+            if (y1) t = a1 * y1[base + c];
+            if (y2) t = fmaf(a2, y2[base + c], t);
+            if (y3) t += y3[base + c];
+            v += t;
+            x[base + c] = v;
+        }
+        if (k < AD_PER) keep[k] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!w1 && !w2) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)W + eps);
+    k = 0;
+    for (int c = threadIdx.x; c < W; c += AD_THREADS, ++k) {
+        const float r = (k < AD_PER ? keep[k] : x[base + c]) * inv;
+        if (w1) h1[base + c] = from_f<T>(r * (w_offset + to_f(w1[c])));
+        if (w2) h2[base + c] = from_f<T>(r * (w_offset + to_f(w2[c])));
+    }
+}
+
+int launch_add_dual_norm(int dt, float* x, const float* y1, float a1, const float* y2, float a2, const float* y3, const void* w1, const void* w2,
+                         float w_offset, float eps, int n, int W, void* h1, void* h2, cudaStream_t s) {
+    if (n <= 0) return WF_OK;
+    if (dt == WF_BF16) add_dual_norm_kernel<<<n, AD_THREADS, 0, s>>>(x, y1, a1, y2, a2, y3, (const __nv_bfloat16*)w1, (const __nv_bfloat16*)w2, w_offset, eps, W, (__nv_bfloat16*)h1, (__nv_bfloat16*)h2);
+    else add_dual_norm_kernel<<<n, AD_THREADS, 0, s>>>(x, y1, a1, y2, a2, y3, (const float*)w1, (const float*)w2, w_offset, eps, W, (float*)h1, (float*)h2);
+    return launch_check(cudaGetLastError(), "add_dual_norm");
 }
 
 // thread per (token, channel)

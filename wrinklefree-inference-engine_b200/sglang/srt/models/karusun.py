@@ -55,6 +55,7 @@ class KarusunConfig:
                 s.rope_dims = int(rot.get("dims", s.rot_dim))
                 s.rope_base = float(rot.get("base", 10000.0))
                 s.scale = float(m["scale"]) if "scale" in m else float((s.dim + s.rot_dim) ** -0.5)
+                s.head_gate = 2                                   # this design gates every output element
             elif L["type"] == "delta":
                 s.type = _lib.WF_SEQ_DELTA
                 s.kv_heads, s.conv = int(m.get("kv_heads", s.heads)), int(m.get("conv", 1))

@@ -112,10 +112,10 @@ _lib = None
 # ---- libwf_seq.so (include/wf_seq.h): the engine for layer-stack sequence models ------------------------------------------------
 SEQ_LIB_PATH = Path(os.environ.get("WF_SEQ_LIB", _PKG_ROOT / "libwf_seq.so"))
 WF_SEQ_F32, WF_SEQ_BF16 = 0, 1
-WF_SEQ_LATENT_ATTENTION, WF_SEQ_DELTA, WF_SEQ_GQA_ATTENTION, WF_SEQ_SSD = 0, 1, 2, 3
-WF_SEQ_BLOCK_SANDWICH, WF_SEQ_BLOCK_POST = 0, 1
+WF_SEQ_LATENT_ATTENTION, WF_SEQ_DELTA, WF_SEQ_GQA_ATTENTION, WF_SEQ_SSD, WF_SEQ_MINGRU, WF_SEQ_MLSTM = 0, 1, 2, 3, 4, 5
+WF_SEQ_BLOCK_SANDWICH, WF_SEQ_BLOCK_POST, WF_SEQ_BLOCK_PARALLEL = 0, 1, 2
 WF_SEQ_FF_NONE, WF_SEQ_FF_ROUTED, WF_SEQ_FF_DENSE = 0, 1, 2
-WF_SEQ_ACT_SILU, WF_SEQ_ACT_CLAMPED, WF_SEQ_ACT_GELU_TANH = 0, 1, 2
+WF_SEQ_ACT_SILU, WF_SEQ_ACT_CLAMPED, WF_SEQ_ACT_GELU_TANH, WF_SEQ_ACT_RELU2 = 0, 1, 2, 3
 WF_SEQ_QKNORM_NONE, WF_SEQ_QKNORM_UNIT, WF_SEQ_QKNORM_HEAD, WF_SEQ_QKNORM_FULL = 0, 1, 2, 3
 
 
@@ -137,6 +137,9 @@ class SeqLayer(C.Structure):
         ("out_norm_groups", C.c_int),
         ("pair", C.c_int), ("mix_scale", C.c_float), ("pair_scale", C.c_float),
         ("tied", C.c_int), ("tied_to", C.c_int),
+        ("q_rank", C.c_int),
+        ("rope_factor", C.c_float), ("rope_orig", C.c_float), ("rope_fast", C.c_float), ("rope_slow", C.c_float),
+        ("v_is_k", C.c_int), ("gate_cap", C.c_float),
     ]
 
     def __init__(self, *a, **kw):
@@ -154,6 +157,7 @@ class SeqConfig(C.Structure):
         ("max_step_tokens", C.c_int),
         ("block_form", C.c_int), ("residual_mult", C.c_float), ("pos_embed", C.c_int), ("pos_base", C.c_float),
         ("n_extra", C.c_int), ("embed_scale", C.c_float), ("norm_weights", C.c_int), ("tied_head", C.c_int),
+        ("norm_offset", C.c_float),
     ]
 
 

@@ -19,6 +19,8 @@ _MODULES: Dict[str, str] = {
     "TutizenForCausalLM": "sglang.srt.models.tutizen",
     "Nukezen": "sglang.srt.models.nukezen",
     "NukezenForCausalLM": "sglang.srt.models.nukezen",
+    "Fivedra": "sglang.srt.models.fivedra",
+    "FivedraForCausalLM": "sglang.srt.models.fivedra",
 }
 
 
