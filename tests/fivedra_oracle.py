@@ -217,3 +217,64 @@ def forward(cfg: Dict, w: Dict[str, torch.Tensor], tokens: List[int], taps: Opti
         if taps is not None:
             taps.append(x.clone())
     return offset_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+MIXERS = {
+    "mingru": lambda h, w, p, m, eps: mingru(h, w, p),
+    "parallel": parallel_mixer,
+    "latent_attention": latent_attention,
+}
+
+
+def random_weights(cfg: Dict, seed: int = 0, sizes: Optional[Dict[int, Dict[str, int]]] = None) -> Dict[str, torch.Tensor]:
+    """Random tensors with the checkpoint's names and shapes, values representable in bfloat16.  `sizes[layer]['rel_rows']` is the row
+    count of a 'parallel' layer's distance-bias table (config.json leaves it to the tensor's shape)."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+    out: Dict[str, torch.Tensor] = {}
+    sizes = sizes or {}
+
+    def mat(name, o, i, s=None):
+        out[name] = (torch.randn(o, i, generator=g) * (s if s is not None else 1.0 / math.sqrt(i))).bfloat16().float()
+
+    def vec(name, n, s=0.1, mean=0.0):
+        out[name] = (mean + torch.randn(n, generator=g) * s).bfloat16().float()
+
+    out["embed"] = (torch.randn(V, W, generator=g) * 0.5).bfloat16().float()
+    vec("final.norm", W, 0.2)
+    mat("head", V, W)
+    for li, L in enumerate(cfg["layers"]):
+        p, m = f"l{li}.", L["mixer"]
+        vec(p + "norm1", W, 0.2)
+        q = p + "mix."
+        if L["type"] == "mingru":
+            C = m["width"]
+            mat(q + "z", C, W); vec(q + "z.b", C, 0.5)
+            mat(q + "x", C, W); vec(q + "x.b", C, 0.5)
+            mat(q + "g", C, W); mat(q + "o", W, C)
+        elif L["type"] == "parallel":
+            a, ql = m["left"], q + "left."
+            H, G, d = a["heads"], a["kv_heads"], a["dim"]
+            mat(ql + "q", H * d, W); vec(ql + "q.b", H * d, 0.3)
+            mat(ql + "k", G * d, W); vec(ql + "k.b", G * d, 0.3)
+            mat(ql + "rel", sizes.get(li, {}).get("rel_rows", 8), H, 1.0)
+            mat(ql + "o", W, H * d)
+            r, qr = m["right"], q + "right."
+            H, d, dv = r["heads"], r["dim"], r["vdim"]
+            mat(qr + "q", H * d, W); mat(qr + "k", H * d, W); mat(qr + "v", H * dv, W); mat(qr + "g", H * dv, W)
+            mat(qr + "i", H, W, 1.5 / math.sqrt(W)); vec(qr + "i.b", H, 0.5)
+            mat(qr + "f", H, W, 1.5 / math.sqrt(W)); vec(qr + "f.b", H, 0.5, 2.0)
+            vec(qr + "norm", H * dv, 0.1, 1.0); mat(qr + "o", W, H * dv)
+        elif L["type"] == "latent_attention":
+            H, d, r, dv, R, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            mat(q + "dq", Q, W); vec(q + "dq.norm", Q, 0.1, 1.0); mat(q + "uq", H * (d + r), Q)
+            mat(q + "dkv", R + r, W); vec(q + "dkv.norm", R, 0.1, 1.0)
+            mat(q + "uk", H * d, R); mat(q + "uv", H * dv, R)
+            vec(q + "sink", H, 1.0); mat(q + "o", W, H * dv)
+        else:
+            raise ValueError(L["type"])
+        f = L.get("mlp")
+        if f is not None:
+            vec(p + "norm2", W, 0.2)
+            mat(p + "mlp.up", f["ff"], W); mat(p + "mlp.down", W, f["ff"])
+    return out
