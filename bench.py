@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """bench.py — decode throughput of the BitNet-2B-4T-shaped hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1|hybrid|tutizen|nukezen]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload bs64|bs1|hybrid|tutizen|nukezen|fivedra]
 
 --workload hybrid (1 GPU) measures the layer-stack sequence engine (latent attention / gated delta rule / routed feed-forward) instead:
 prefill and decode tok/s at two layer sizes with random weights, per launch-group times, and the BitNet engine at equal size beside it.
@@ -1066,6 +1066,74 @@ def run_nukezen(args):
           "hbm_peak_gbs": peak, "peak_source": peak_src, "sizes": out, "clocks": clocks, "gpu_launches": launches})
     return 0
 
+# --workload fivedra: the Fivedra design (parallel two-norm blocks; latent attention with query latent, interpolated rotation and learned
+# sinks; an element-wise gated recurrence; window attention whose values are its keys beside a matrix memory with exponential gating;
+# ungated relu^2 units) on the sequence engine at sizes that resemble real layers, random weights, beside the closest existing model on
+# the same engine at equal width / heads / layers / feed-forward size: Nukezen (paired window attention + recurrence, dense units).
+FIVEDRA_SIZES = {
+    "w1024": dict(lat=dict(heads=8, d=64, r=32, dv=64, R=256, Q=384), gru=1024, mem=dict(heads=8, d=64, dv=128)),
+    "w2560": dict(lat=dict(heads=20, d=96, r=32, dv=128, R=512, Q=768), gru=2560, mem=dict(heads=20, d=128, dv=128)),
+}
+
+
+def fivedra_config(z, f):
+    """z: the Nukezen size of the same name (width, heads, window, feed-forward, vocabulary), f: what only this design has"""
+    t, g = f["lat"], f["mem"]
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    lat = {"type": "latent_attention", "mixer": {"heads": t["heads"], "dim": t["d"], "rot_dim": t["r"], "vdim": t["dv"], "kv_rank": t["R"], "q_rank": t["Q"],
+                                                  "scale": (t["d"] + t["r"]) ** -0.5,
+                                                  "rot": {"dims": t["r"], "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}, "mlp": dense}
+    gru = {"type": "mingru", "mixer": {"width": f["gru"]}, "mlp": dense}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["d"], "vdim": z["d"], "scale": z["d"] ** -0.5, "mask": {"size": z["window"]}, "bias_max": 2 * z["window"]}
+    right = {"heads": g["heads"], "dim": g["d"], "vdim": g["dv"], "gate_cap": 15.0}
+    par = {"type": "parallel", "mixer": {"left": left, "left_scale": 0.7, "right": right, "right_scale": 0.7}, "mlp": dense}
+    layers, shapes = [], {}
+    for i in range(z["layers"]):
+        L = (lat, gru, par, par)[i % 4]
+        layers.append(L)
+        if L["type"] == "parallel":
+            shapes[f"l{i}.mix.left.rel"] = (z["rel_rows"], z["heads"])
+    cfg = {"architecture": "Fivedra", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": layers}
+    return cfg, shapes
+
+
+def run_fivedra(args):
+    from wf_bitnet import _lib
+    torch.cuda.set_device(0)
+    _lib.require_gpu()
+    K, W_ = max(2, args.steps), max(3, args.warmup)
+    peak, peak_src = measured_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    out, launches = {}, 0
+    for name, f in FIVEDRA_SIZES.items():
+        if args.hybrid_size and name != args.hybrid_size:
+            continue
+        z = NUKEZEN_SIZES[name]
+        prompt = 2048
+        decode_points = [(1, 512), (8, 2048), (64, 4096)] if name == "w2560" else [(1, 512), (8, 1024), (64, 1024)]
+        cfg, shapes = fivedra_config(z, f)
+        res, n1 = measure_seq_model(cfg, prompt, decode_points, K, shapes)
+        res["layer_kinds"] = [L["type"] + " + dense" for L in cfg["layers"]]
+        t, g = f["lat"], f["mem"]
+        # state one decoded token reads and writes per recurrent mixer (float); cached bytes per attention layer and 1000 tokens of context
+        res["state_bytes"] = {"mingru": 4 * f["gru"], "matrix_memory": 4 * g["heads"] * (g["d"] * (g["dv"] + 1) + 1)}
+        res["cache_bytes_per_layer_per_1k_ctx"] = {"latent": 1000 * (t["R"] + t["r"]) * 2, "window (keys only)": 1000 * z["kv_heads"] * z["d"] * 2}
+        ncfg, nshapes = nukezen_config(z)
+        nres, n2 = measure_seq_model(ncfg, prompt, decode_points, K, nshapes)
+        res["nukezen_equal_size"] = nres
+        launches += n1 + n2
+        out[name] = res
+    clocks = sampler.stop()
+    head = out.get("w2560") or next(iter(out.values()))
+    top = sorted(head["decode"].items())[-1]
+    emit({"metric": "prefill / decode tok/s of the Fivedra design on the sequence engine beside Nukezen at equal size", "workload": "fivedra",
+          "value": top[1]["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W_, "higher_is_better": True, "dtype": "bf16",
+          "data": "synthetic (random weights; decode contexts are whatever the cache pages hold)", "vs_baseline": None,
+          "config": {"model": "Fivedra-shaped, " + ", ".join(out), "point": top[0], "l2": "weights per step exceed L2 (126 MB) at w2560; w1024 is L2-resident"},
+          "hbm_peak_gbs": peak, "peak_source": peak_src, "sizes": out, "clocks": clocks, "gpu_launches": launches})
+    return 0
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -1073,17 +1141,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1", "hybrid", "tutizen", "nukezen"] + sorted(TP_WORKLOADS))
-    ap.add_argument("--hybrid-size", default="", help="--workload hybrid / tutizen / nukezen: run only this size (w1024 | w2560)")
+    ap.add_argument("--workload", default="bs64", choices=["bs64", "bs1", "hybrid", "tutizen", "nukezen", "fivedra"] + sorted(TP_WORKLOADS))
+    ap.add_argument("--hybrid-size", default="", help="--workload hybrid / tutizen / nukezen / fivedra: run only this size (w1024 | w2560)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-aux", action="store_true", help="skip the batch-1 aux measurement")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel suite (aux.tp)")
     args = ap.parse_args()
-    if args.workload in ("hybrid", "tutizen", "nukezen"):
+    if args.workload in ("hybrid", "tutizen", "nukezen", "fivedra"):
         if args.impl == "reference":
             emit({"impl": "reference", "unavailable": "the reference has no model of this design; its arm is defined for the 2B workloads only"})
             return 0
-        return {"hybrid": run_hybrid, "tutizen": run_tutizen, "nukezen": run_nukezen}[args.workload](args)
+        return {"hybrid": run_hybrid, "tutizen": run_tutizen, "nukezen": run_nukezen, "fivedra": run_fivedra}[args.workload](args)
     if args.workload in TP_WORKLOADS:
         if args.impl == "reference":
             emit({"impl": "reference", "unavailable": "the reference arm is defined for the 2B workloads (bs64 / bs1) only"})

@@ -4,7 +4,7 @@
 //    and cuts the portion into time slices, one per warp: every slice first reduces itself to the pair (A, B) with S_end = A S_start + B,
 //    the pairs are chained through shared memory, and every slice runs again from its start state for the outputs.
 //  * matrix memory with exponential gating (mLSTM form): the log gates and their running maximum m_t = max(f_t + m_(t-1), i_t) are a
-//    max-plus linear recurrence, scanned 32 tokens at a time by one warp per (sequence, head); the matrix recurrence itself then is the
+//    max-plus linear recurrence, scanned by a block per (sequence, head) whose warps take 32 tokens each; the matrix recurrence itself then is the
 //    plain decayed outer-product accumulation of seq_delta.cu with keep = exp(f + m' - m) and put = exp(i - m), its normaliser n riding
 //    along as one more value column.  The read-out (division, per-head unit RMS, weight, sigmoid gate) is one more row kernel.
 // Gates, decays, exponentials, maxima and state are float in both storage modes.
@@ -18,15 +18,7 @@ namespace {
 
 constexpr int MG_MAXW = 16;     // most time slices (warps) of a block
 
-template <typename T>
-__device__ __forceinline__ void mingru_gate(const float* __restrict__ row, int z_off, int x_off, int c, const T* __restrict__ zb, const T* __restrict__ xb,
-                                            float* keep, float* put) {
-    const float z = sigmoid_f(row[z_off + c] + to_f(zb[c]));
-    const float u = row[x_off + c] + to_f(xb[c]);
-    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-    *keep = 1.f - z;
-    *put = z * cand;
-}
+constexpr int MG_UN = 8;        // tokens whose inputs are loaded before any of them is used: the loads do not wait for the chain
 
 template <typename T>
 __global__ void __launch_bounds__(32 * MG_MAXW) mingru_kernel(Batch b, int C, const float* __restrict__ proj, int ld, int z_off, int x_off, int g_off,
@@ -40,16 +32,25 @@ __global__ void __launch_bounds__(32 * MG_MAXW) mingru_kernel(Batch b, int C, co
     const int per = (len + nw - 1) / nw;
     const int t0 = w * per < len ? w * per : len, t1 = t0 + per < len ? t0 + per : len;
     float* Sp = state + (size_t)b.seq_slot[sq] * slot_stride + c;
+    const float bz = ok ? to_f(zb[c]) : 0.f, bx = ok ? to_f(xb[c]) : 0.f;
+    const float* base = proj + (size_t)start * ld + c;
     float S = 0.f;
     if (nw > 1) {
         // this slice as one affine map
         float A = 1.f, B = 0.f;
         if (ok)
-            for (int t = t0; t < t1; ++t) {
-                float keep, put;
-                mingru_gate(proj + (size_t)(start + t) * ld, z_off, x_off, c, zb, xb, &keep, &put);
-                A *= keep;
-                B = fmaf(keep, B, put);
+            for (int t = t0; t < t1; t += MG_UN) {
+                float zr[MG_UN], xr[MG_UN];
+#pragma unroll
+                for (int k = 0; k < MG_UN; ++k) { const bool in = t + k < t1; zr[k] = in ? base[(size_t)(t + k) * ld + z_off] : 0.f; xr[k] = in ? base[(size_t)(t + k) * ld + x_off] : 0.f; }
+#pragma unroll
+                for (int k = 0; k < MG_UN; ++k) {
+                    if (t + k >= t1) break;
+                    const float z = sigmoid_f(zr[k] + bz), u = xr[k] + bx;
+                    const float keep = 1.f - z, put = z * (u >= 0.f ? u + 0.5f : sigmoid_f(u));
+                    A *= keep;
+                    B = fmaf(keep, B, put);
+                }
             }
         sA[w][lane] = A; sB[w][lane] = B;
         __syncthreads();
@@ -59,33 +60,46 @@ __global__ void __launch_bounds__(32 * MG_MAXW) mingru_kernel(Batch b, int C, co
         }
     } else if (ok) S = *Sp;
     if (!ok) return;
-    for (int t = t0; t < t1; ++t) {
-        const float* row = proj + (size_t)(start + t) * ld;
-        float keep, put;
-        mingru_gate(row, z_off, x_off, c, zb, xb, &keep, &put);
-        S = fmaf(keep, S, put);
-        out[(size_t)(start + t) * C + c] = from_f<T>(S * silu_f(row[g_off + c]));
+    for (int t = t0; t < t1; t += MG_UN) {
+        float zr[MG_UN], xr[MG_UN], gr[MG_UN];
+#pragma unroll
+        for (int k = 0; k < MG_UN; ++k) {
+            const bool in = t + k < t1;
+            const float* row = base + (size_t)(t + k) * ld;
+            zr[k] = in ? row[z_off] : 0.f; xr[k] = in ? row[x_off] : 0.f; gr[k] = in ? row[g_off] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < MG_UN; ++k) {
+            if (t + k >= t1) break;
+            const float z = sigmoid_f(zr[k] + bz), u = xr[k] + bx;
+            S = fmaf(1.f - z, S, z * (u >= 0.f ? u + 0.5f : sigmoid_f(u)));
+            out[(size_t)(start + t + k) * C + c] = from_f<T>(S * silu_f(gr[k]));
+        }
     }
     if (t1 == len && (t0 < t1 || w == 0)) *Sp = S;     // the slice that ends the portion leaves the state (empty slices behind it hold nothing)
 }
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
+constexpr int ML_MAXW = 32;
+
+// One block per (sequence, head); its warps take 32 tokens each, side by side.  A token is the map m -> max(F + m, I) (F = log forget gate,
+// I = log input gate); maps compose as (F1, I1) then (F2, I2) = (F1 + F2, max(F2 + I1, I2)).  Each warp scans its 32 maps with shuffles,
+// the warps' totals are chained through shared memory, and the block walks the portion in rounds of 32 tokens per warp.
 template <typename T>
-__global__ void mlstm_gates_kernel(Batch b, int H, const float* __restrict__ proj, int ld, int i_off, int f_off, const T* __restrict__ ib, const T* __restrict__ fb,
-                                   float cap, float* __restrict__ mstate, size_t slot_stride, float* __restrict__ keep, float* __restrict__ put,
-                                   float* __restrict__ mrun) {
-    const int sq = blockIdx.x, lane = threadIdx.x & 31;
-    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (h >= H) return;
+__global__ void __launch_bounds__(32 * ML_MAXW) mlstm_gates_kernel(Batch b, int H, const float* __restrict__ proj, int ld, int i_off, int f_off,
+                                                                     const T* __restrict__ ib, const T* __restrict__ fb, float cap, float* __restrict__ mstate,
+                                                                     size_t slot_stride, float* __restrict__ keep, float* __restrict__ put, float* __restrict__ mrun) {
+    __shared__ float totF[ML_MAXW], totI[ML_MAXW];
+    const int sq = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int start = b.seq_start[sq], len = b.seq_len[sq];
     float* mp = mstate + (size_t)b.seq_slot[sq] * slot_stride + h;
-    float m = *mp;
+    float m = *mp;                          // every thread carries the block's running maximum
     const float bi = to_f(ib[h]), bf = to_f(fb[h]);
-    for (int t0 = 0; t0 < len; t0 += 32) {
-        const int t = t0 + lane;
+    for (int r0 = 0; r0 < len; r0 += 32 * nw) {
+        const int t = r0 + w * 32 + lane;
         const bool ok = t < len;
-        // a token is the map m -> max(F + m, I); tokens beyond the portion are the identity (F = 0, I = -inf)
+        // tokens beyond the portion are the identity (F = 0, I = -inf)
         float li = -INFINITY, lf = 0.f;
         if (ok) {
             const float* row = proj + (size_t)(start + t) * ld;
@@ -95,22 +109,31 @@ __global__ void mlstm_gates_kernel(Batch b, int H, const float* __restrict__ pro
         }
         float F = lf, I = li;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {       // inclusive scan: (F1, I1) then (F2, I2) is (F1 + F2, max(F2 + I1, I2))
+        for (int o = 1; o < 32; o <<= 1) {
             const float Fp = __shfl_up_sync(0xffffffffu, F, o), Ip = __shfl_up_sync(0xffffffffu, I, o);
             if (lane >= o) { I = fmaxf(F + Ip, I); F = F + Fp; }
         }
-        const float mt = fmaxf(F + m, I);
+        if (nw > 1) {
+            if (lane == 31) { totF[w] = F; totI[w] = I; }
+            __syncthreads();
+        }
+        float m_in = m;                     // the maximum before this warp's first token
+        for (int v = 0; v < w; ++v) m_in = fmaxf(totF[v] + m_in, totI[v]);
+        const float mt = fmaxf(F + m_in, I);
         float mprev = __shfl_up_sync(0xffffffffu, mt, 1);
-        if (lane == 0) mprev = m;
+        if (lane == 0) mprev = m_in;
         if (ok) {
             const size_t at = (size_t)(start + t) * H + h;
             keep[at] = expf(lf + mprev - mt);
             put[at] = expf(li - mt);
             mrun[at] = mt;
         }
-        m = __shfl_sync(0xffffffffu, mt, 31);
+        if (nw > 1) {
+            for (int v = 0; v < nw; ++v) m = fmaxf(totF[v] + m, totI[v]);
+            __syncthreads();                // the totals are overwritten in the next round
+        } else m = __shfl_sync(0xffffffffu, mt, 31);
     }
-    if (lane == 0) *mp = m;
+    if (threadIdx.x == 0) *mp = m;
 }
 
 // one warp per (token, head)
@@ -151,10 +174,11 @@ int launch_mingru(int dt, const Batch& b, int C, const float* proj, int ld, int 
 int launch_mlstm_gates(int dt, const Batch& b, int H, const float* proj, int ld, int i_off, int f_off, const void* ib, const void* fb, float cap,
                        float* mstate, size_t slot_stride, float* keep, float* put, float* mrun, cudaStream_t s) {
     if (b.nseq <= 0) return WF_OK;
-    const int warps = H < 4 ? H : 4;
-    const dim3 grid(b.nseq, (H + warps - 1) / warps);
-    if (dt == WF_BF16) mlstm_gates_kernel<<<grid, 32 * warps, 0, s>>>(b, H, proj, ld, i_off, f_off, (const __nv_bfloat16*)ib, (const __nv_bfloat16*)fb, cap, mstate, slot_stride, keep, put, mrun);
-    else mlstm_gates_kernel<<<grid, 32 * warps, 0, s>>>(b, H, proj, ld, i_off, f_off, (const float*)ib, (const float*)fb, cap, mstate, slot_stride, keep, put, mrun);
+    int nw = (b.max_len + 31) / 32;
+    nw = nw < 1 ? 1 : (nw > ML_MAXW ? ML_MAXW : nw);
+    const dim3 grid(b.nseq, H);
+    if (dt == WF_BF16) mlstm_gates_kernel<<<grid, 32 * nw, 0, s>>>(b, H, proj, ld, i_off, f_off, (const __nv_bfloat16*)ib, (const __nv_bfloat16*)fb, cap, mstate, slot_stride, keep, put, mrun);
+    else mlstm_gates_kernel<<<grid, 32 * nw, 0, s>>>(b, H, proj, ld, i_off, f_off, (const float*)ib, (const float*)fb, cap, mstate, slot_stride, keep, put, mrun);
     return launch_check(cudaGetLastError(), "mlstm_gates");
 }
 

@@ -189,7 +189,7 @@ int launch_ssd_post(int dt, int n, int H, int dv, int groups, const float* o, co
 // Long portions are cut into time slices that run in parallel inside a block (the recurrence is linear in S).
 int launch_mingru(int dt, const Batch& b, int C, const float* proj, int ld, int z_off, int x_off, int g_off, const void* zb, const void* xb,
                   float* state, size_t slot_stride, void* out, cudaStream_t s);
-// log gates of the matrix memory and their running maximum, per (sequence, head) in token order (a warp scans 32 tokens at a time):
+// log gates of the matrix memory and their running maximum, per (sequence, head) in token order (a block's warps scan 32 tokens each):
 // li = cap tanh((proj[i_off + h] + ib[h]) / cap), lf = logsigmoid(cap tanh((proj[f_off + h] + fb[h]) / cap)) (cap <= 0: no cap);
 // m_t = max(lf + m_(t-1), li) with m carried in mstate[slot * slot_stride + h]; keep[n, H] = exp(lf + m_(t-1) - m_t),
 // put[n, H] = exp(li - m_t), mrun[n, H] = m_t.
