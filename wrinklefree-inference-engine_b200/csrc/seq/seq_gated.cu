@@ -1,7 +1,7 @@
 // Gated recurrences whose gates read only the current token, so that everything but a short linear chain runs in parallel over time.
 //
-//  * element-wise recurrence (minGRU form): S_t = (1 - z_t) S_(t-1) + z_t c_t per channel.  A block owns 32 channels of one sequence
-//    and cuts the portion into time slices, one per warp: every slice first reduces itself to the pair (A, B) with S_end = A S_start + B,
+//  * element-wise recurrence (minGRU form): S_t = (1 - z_t) S_(t-1) + z_t c_t per channel.  A block owns 32 (or 8) channels of one sequence
+//    and cuts the portion into time slices, up to 64 of them: every slice first reduces itself to the pair (A, B) with S_end = A S_start + B,
 //    the pairs are chained through shared memory, and every slice runs again from its start state for the outputs.
 //  * matrix memory with exponential gating (mLSTM form): the log gates and their running maximum m_t = max(f_t + m_(t-1), i_t) are a
 //    max-plus linear recurrence, scanned by a block per (sequence, head) whose warps take 32 tokens each; the matrix recurrence itself then is the
@@ -20,13 +20,15 @@ constexpr int MG_MAXW = 16;     // most time slices (warps) of a block
 
 constexpr int MG_UN = 8;        // tokens whose inputs are loaded before any of them is used: the loads do not wait for the chain
 
+// ch: channels of a block (a power of two up to 32); a warp holds 32 / ch time slices of them.  Few channels per block make more blocks
+// and more slices when one long portion has to fill the machine; 8 floats are still a whole 32-byte sector of a row.
 template <typename T>
-__global__ void __launch_bounds__(32 * MG_MAXW) mingru_kernel(Batch b, int C, const float* __restrict__ proj, int ld, int z_off, int x_off, int g_off,
+__global__ void __launch_bounds__(32 * MG_MAXW) mingru_kernel(Batch b, int C, int ch, const float* __restrict__ proj, int ld, int z_off, int x_off, int g_off,
                                                                 const T* __restrict__ zb, const T* __restrict__ xb, float* __restrict__ state,
                                                                 size_t slot_stride, T* __restrict__ out) {
-    __shared__ float sA[MG_MAXW][32], sB[MG_MAXW][32];
-    const int sq = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int c = blockIdx.y * 32 + lane;
+    __shared__ float sA[32 * MG_MAXW], sB[32 * MG_MAXW];       // [slice][ch]
+    const int sq = blockIdx.x, cl = threadIdx.x % ch, w = threadIdx.x / ch, nw = blockDim.x / ch;      // w: this thread's time slice of nw
+    const int c = blockIdx.y * ch + cl;
     const bool ok = c < C;
     const int start = b.seq_start[sq], len = b.seq_len[sq];
     const int per = (len + nw - 1) / nw;
@@ -52,11 +54,11 @@ __global__ void __launch_bounds__(32 * MG_MAXW) mingru_kernel(Batch b, int C, co
                     B = fmaf(keep, B, put);
                 }
             }
-        sA[w][lane] = A; sB[w][lane] = B;
+        sA[w * ch + cl] = A; sB[w * ch + cl] = B;
         __syncthreads();
         if (ok) {
             S = *Sp;
-            for (int v = 0; v < w; ++v) S = fmaf(sA[v][lane], S, sB[v][lane]);
+            for (int v = 0; v < w; ++v) S = fmaf(sA[v * ch + cl], S, sB[v * ch + cl]);
         }
     } else if (ok) S = *Sp;
     if (!ok) return;
@@ -162,12 +164,15 @@ int launch_mingru(int dt, const Batch& b, int C, const float* proj, int ld, int 
                   float* state, size_t slot_stride, void* out, cudaStream_t s) {
     if (b.nseq <= 0) return WF_OK;
     if (C <= 0) { set_error("mingru: %d channels", C); return WF_ERR_INVALID; }
-    // slices of at least 8 tokens; a block of single decoded tokens is one warp
-    int nw = b.max_len / 8;
+    // slices of at least 8 tokens; a block of single decoded tokens is one warp of 32 channels.  When long portions of few sequences
+    // would leave most of the machine idle, a block takes 8 channels only: four times the blocks and, per warp, four times the slices.
+    int ch = 32;
+    if (b.max_len >= 256 && (long long)b.nseq * ((C + 31) / 32) < 2 * sm_count()) ch = 8;
+    int nw = b.max_len / (8 * (32 / ch));
     nw = nw < 1 ? 1 : (nw > MG_MAXW ? MG_MAXW : nw);
-    const dim3 grid(b.nseq, (C + 31) / 32);
-    if (dt == WF_BF16) mingru_kernel<<<grid, 32 * nw, 0, s>>>(b, C, proj, ld, z_off, x_off, g_off, (const __nv_bfloat16*)zb, (const __nv_bfloat16*)xb, state, slot_stride, (__nv_bfloat16*)out);
-    else mingru_kernel<<<grid, 32 * nw, 0, s>>>(b, C, proj, ld, z_off, x_off, g_off, (const float*)zb, (const float*)xb, state, slot_stride, (float*)out);
+    const dim3 grid(b.nseq, (C + ch - 1) / ch);
+    if (dt == WF_BF16) mingru_kernel<<<grid, 32 * nw, 0, s>>>(b, C, ch, proj, ld, z_off, x_off, g_off, (const __nv_bfloat16*)zb, (const __nv_bfloat16*)xb, state, slot_stride, (__nv_bfloat16*)out);
+    else mingru_kernel<<<grid, 32 * nw, 0, s>>>(b, C, ch, proj, ld, z_off, x_off, g_off, (const float*)zb, (const float*)xb, state, slot_stride, (float*)out);
     return launch_check(cudaGetLastError(), "mingru");
 }
 
