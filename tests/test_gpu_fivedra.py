@@ -483,6 +483,53 @@ def test_tensor_core_attention_with_key_splits_in_a_ragged_batch():
         m.close()
 
 
+def _random_config(rng):
+    """1-5 layers of random kinds with sizes drawn independently of each other"""
+    W = rng.choice([24, 40, 72, 96, 136, 200])
+    layers, sizes = [], {}
+    for i in range(rng.randint(1, 5)):
+        ff = rng.choice([None, W, rng.randint(8, 3 * W)])
+        kind = rng.choice(["mingru", "parallel", "latent_attention"])
+        if kind == "mingru":
+            layers.append(gru(width=rng.choice([W, rng.randint(5, 2 * W)]), ff=ff))
+        elif kind == "parallel":
+            G, rep, B = rng.choice([1, 2, 3]), rng.choice([1, 2, 4, 8]), rng.choice([4, 10, 16, 24])
+            d = rng.choice([6, 16, 24, 64, 128, 192])
+            layers.append(par(heads=G * rep, kv=G, dim=d, scale=rng.choice([d ** -0.5, 0.2]), window=rng.choice([1, 2, 7, 16, 50, 120]), far=rng.choice([B // 2 + 1, 3 * B, 100.5]),
+                              ls=rng.choice([0.6, 1.0, -0.4]), rs=rng.choice([0.5, 1.3]), mh=rng.choice([1, 2, 5]), md=rng.choice([4, 16, 33, 72, 160]), mv=rng.choice([4, 24, 40, 136]),
+                              cap=rng.choice([1.5, 9.0, 25.0]), ff=ff))
+            sizes[i] = {"rel_rows": B}
+        else:
+            r, d = rng.choice([2, 4, 12, 32, 48]), rng.choice([8, 24, 40, 64])
+            sc = rng.choice([None, (rng.choice([2.0, 8.0]), rng.choice([16, 200]), rng.choice([32.0, 8.0]), rng.choice([1.0, 0.5]))])
+            layers.append(lat(heads=rng.choice([1, 2, 5, 12, 33, 40]), dim=d, rot=r, vdim=rng.choice([8, 20, 48]), rank=rng.choice([16, 40, 96, 256]), qrank=rng.choice([8, 36, 100]),
+                              scale=rng.choice([(d + r) ** -0.5, 0.1]), base=rng.choice([100.0, 10000.0, 5e5]), scaling=sc, ff=ff))
+    return config(layers, width=W, vocab=rng.choice([50, 97, 300]), eps=rng.choice([1e-6, 1e-4]), escale=rng.choice([1.0, W ** 0.5, 0.3])), sizes
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_configurations(seed):
+    """Layer orders, head counts, sizes, windows and constants drawn at random: one prompt whole, prompt + decoded tail, and in random
+    portions, in both dtypes."""
+    import random
+    rng = random.Random(1000 + seed)
+    cfg, sizes = _random_config(rng)
+    n = rng.choice([3, 17, 64, 130, 290])
+    w = make_weights((cfg, sizes), 200 + seed)
+    toks = tokens_for(cfg, n, 300 + seed)
+    want = oracle_logits(cfg, w, toks)
+    k = max(1, n - rng.randint(1, 8))
+    cuts, left = [], n
+    while left:
+        cuts.append(min(left, rng.choice([1, 2, 3, 5, 16, 33, 64, 100])))
+        left -= cuts[-1]
+    for dtype in ("float32", "bfloat16"):
+        m = build(cfg, w, dtype, max_tokens=512, page_size=rng.choice([4, 16, 64]), max_step_tokens=512)
+        for c in ([n], [k] + [1] * (n - k), cuts):
+            assert_close(run_alone(m, toks, c), want, dtype, (seed, dtype, c[:4]), 1.5)
+        m.close()
+
+
 # ------------------------------------------------------------------------------------------------- scheduler and command line
 def _greedy_matches(cfg, w, prompt, output):
     seq = list(prompt)
