@@ -87,7 +87,7 @@ constexpr int ML_MAXW = 32;
 
 // One block per (sequence, head); its warps take 32 tokens each, side by side.  A token is the map m -> max(F + m, I) (F = log forget gate,
 // I = log input gate); maps compose as (F1, I1) then (F2, I2) = (F1 + F2, max(F2 + I1, I2)).  Each warp scans its 32 maps with shuffles,
-// the warps' totals are chained through shared memory, and the block walks the portion in rounds of 32 tokens per warp.
+// the warps' totals are chained through shared memory, and the block walks the portion in passes of 32 tokens per warp.
 template <typename T>
 __global__ void __launch_bounds__(32 * ML_MAXW) mlstm_gates_kernel(Batch b, int H, const float* __restrict__ proj, int ld, int i_off, int f_off,
                                                                      const T* __restrict__ ib, const T* __restrict__ fb, float cap, float* __restrict__ mstate,
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(32 * ML_MAXW) mlstm_gates_kernel(Batch b, int 
         }
         if (nw > 1) {
             for (int v = 0; v < nw; ++v) m = fmaxf(totF[v] + m, totI[v]);
-            __syncthreads();                // the totals are overwritten in the next round
+            __syncthreads();                // the totals are overwritten in the next pass
         } else m = __shfl_sync(0xffffffffu, mt, 31);
     }
     if (threadIdx.x == 0) *mp = m;
